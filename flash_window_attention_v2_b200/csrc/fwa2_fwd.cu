@@ -1,0 +1,586 @@
+// Forward kernel: fused L2-normalisation of Q and K, cosine scores on the tcgen05 tensor cores
+// (accumulators in tensor memory), per-head clamped logit scale, relative-position bias,
+// shifted-window mask, online softmax, P*V and the log-sum-exp, in one pass.
+//
+// One persistent CTA handles a sequence of jobs (one unit, or two units of <= 64 tokens).  Roles:
+//   warps 0-3  softmax: thread t owns query row t of the current 128-row tile
+//   warp  4    issues every tcgen05.mma (one thread)
+//   warp  5    TMA producer (one thread): K, V, Q tiles and the bias / mask table chunks
+// Replaces flash_win_attn_v2/kernels/attn_kernel_forward.py:21-258 (`_fwd_kernel`).
+#include "fwa2_common.cuh"
+
+namespace fwa2 {
+
+constexpr int kFwdThreads = 192;
+constexpr uint32_t kFwdTmemCols = 256;
+constexpr uint32_t kTmemS = 0;      // scores: two 64-column step buffers (one 128-column tile in pair mode)
+constexpr uint32_t kTmemPV = 128;   // 32 columns: P*V of one step
+constexpr uint32_t kTmemP = 160;    // packed P: 32 columns per step (64 in pair mode)
+
+enum FwdBar : int {
+  kBarKvFull = 0, kBarKvReady = 2, kBarKvFree = 4,
+  kBarQFull = 6, kBarQReady = 8, kBarQFree = 10,
+  kBarSFull = 12, kBarSFree = 14,
+  kBarBmFull = 16, kBarBmFree = 20,
+  kBarPFull = 24, kBarPvDone = 25,
+  kFwdNumBars = 26
+};
+
+struct FwdShape {
+  int N, H, U, pair, MT, KS, rows_kv;
+};
+
+__device__ __forceinline__ FwdShape fwd_shape(const FwdParams& p) {
+  FwdShape s;
+  s.N = p.N;
+  s.H = p.H;
+  s.U = p.BW * p.H;
+  s.pair = p.pair_mode;
+  s.MT = s.pair ? 1 : (p.N + kTileRows - 1) / kTileRows;
+  s.KS = s.pair ? 1 : (p.N + kStepCols - 1) / kStepCols;
+  s.rows_kv = s.pair ? 128 : ((p.N + 63) / 64) * 64;
+  return s;
+}
+
+// Normalise one 32-element row of a 64-byte-swizzled tile in place; returns 1 / max(|x|, 1e-12).
+template <typename T>
+__device__ __forceinline__ float normalise_row(uint32_t tile_base, uint32_t row) {
+  uint32_t w[4][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    lds128(tile_base + sw64_offset(row, ch), w[ch]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = Elem<T>::lo(w[ch][i]), b = Elem<T>::hi(w[ch][i]);
+      ss = fmaf(a, a, ss);
+      ss = fmaf(b, b, ss);
+    }
+  }
+  const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      w[ch][i] = Elem<T>::pack(Elem<T>::lo(w[ch][i]) * rn, Elem<T>::hi(w[ch][i]) * rn);
+    sts128(tile_base + sw64_offset(row, ch), w[ch]);
+  }
+  return rn;
+}
+
+template <typename T>
+__device__ __forceinline__ float load_scale(const FwdParams& p, int h) {
+  if (!p.scale_is_tensor) return *static_cast<const float*>(p.scale);
+  const float g = Elem<T>::from_raw(static_cast<const uint16_t*>(p.scale)[h]);
+  return __expf(fminf(g, kLn100));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Softmax warps
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool kPTmem>
+__device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_t bars,
+                                 uint32_t tmem, const WaitCtx& ctx) {
+  const FwdShape sh = fwd_shape(p);
+  const uint32_t tid = threadIdx.x;          // 0..127 = row of the tile
+  const uint32_t hf = tid >> 6;
+  const uint32_t lane_base = ((tid >> 5) * 32u) << 16;
+  const bool any_table = p.has_bias || p.has_mask;
+  auto bar = [&](int i) { return bars + 8u * i; };
+
+  if (sh.pair) {
+    // The half of P that belongs to the other unit of the pair stays zero for the whole kernel.
+    if constexpr (kPTmem) {
+      uint32_t z[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) z[i] = 0u;
+      tmem_st16(tmem + lane_base + kTmemP + (hf ^ 1u) * 32u, z);
+      tmem_st16(tmem + lane_base + kTmemP + (hf ^ 1u) * 32u + 16u, z);
+      tmem_wait_st();
+    } else {
+      const uint32_t z[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        sts128(smem_base + p.off_p + (hf ^ 1u) * 16384u + sw128_offset(tid, ch), z);
+    }
+  }
+
+  uint32_t jt = 0, tt = 0, sc = 0, cc = 0, pvc = 0;
+  const uint32_t nsb = sh.pair ? 1u : 2u;
+  for (int job = blockIdx.x; job < p.n_jobs; job += gridDim.x, ++jt) {
+    const int unit = sh.pair ? 2 * job + static_cast<int>(hf) : job;
+    const bool unit_ok = unit < sh.U;
+    const int bw = unit / sh.H, h = unit - bw * sh.H;
+    const float scale = load_scale<T>(p, h);
+
+    // ---- normalise the K rows of this job in place ----
+    const uint32_t kvs = jt % p.n_kv_stages;
+    const uint32_t kv_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
+    if (!mbar_wait(bar(kBarKvFull + kvs), (jt / p.n_kv_stages) & 1u, ctx, 10)) return;
+    for (uint32_t rr = tid; rr < static_cast<uint32_t>(sh.rows_kv); rr += 128u)
+      normalise_row<T>(kv_base, rr);
+    fence_proxy_async_smem();
+    mbar_arrive(bar(kBarKvReady + kvs));
+
+    for (int mt = 0; mt < sh.MT; ++mt, ++tt) {
+      // ---- normalise my Q row ----
+      const uint32_t qs = tt & 1u;
+      const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
+      if (!mbar_wait(bar(kBarQFull + qs), (tt >> 1) & 1u, ctx, 11)) return;
+      normalise_row<T>(q_base, tid);
+      fence_proxy_async_smem();
+      mbar_arrive(bar(kBarQReady + qs));
+
+      const int row = sh.pair ? static_cast<int>(tid & 63u) : mt * kTileRows + static_cast<int>(tid);
+      const bool row_ok = unit_ok && row < sh.N;
+
+      float m_run = -INFINITY, l_run = 0.f, alpha_pend = 0.f;
+      float acc[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+
+      for (int s = 0; s < sh.KS; ++s, ++sc) {
+        const int ncols = sh.pair ? sh.N : min(kStepCols, sh.N - s * kStepCols);
+        // ---- scores of this step out of tensor memory ----
+        const uint32_t sb = sc % nsb;
+        if (!mbar_wait(bar(kBarSFull + sb), (sc / nsb) & 1u, ctx, 12)) return;
+        tc_fence_after();
+        float x[64];
+        {
+          const uint32_t col = kTmemS + (sh.pair ? hf * 64u : sb * 64u);
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tmem + lane_base + col, r0);
+          tmem_ld32(tmem + lane_base + col + 32u, r1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            x[i] = __uint_as_float(r0[i]);
+            x[32 + i] = __uint_as_float(r1[i]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar(kBarSFree + sb));
+
+        // ---- x = scale * cos + bias + mask ----
+        if (any_table) {
+          const int nch = ncols > kChunkCols ? 2 : 1;
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            if (c2 < nch) {
+              const uint32_t st = cc % p.n_bm_stages;
+              const uint32_t bm_base = smem_base + p.off_bm + st * (2u * kTableTileBytes);
+              if (!mbar_wait(bar(kBarBmFull + st), (cc / p.n_bm_stages) & 1u, ctx, 13)) return;
+#pragma unroll
+              for (int ch = 0; ch < 4; ++ch) {
+                uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
+                if (p.has_bias) lds128(bm_base + sw64_offset(tid, ch), wb);
+                if (p.has_mask) lds128(bm_base + kTableTileBytes + sw64_offset(tid, ch), wm);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int j = c2 * 32 + ch * 8 + i * 2;
+                  x[j] = fmaf(x[j], scale, Elem<T>::lo(wb[i])) + Elem<T>::lo(wm[i]);
+                  x[j + 1] = fmaf(x[j + 1], scale, Elem<T>::hi(wb[i])) + Elem<T>::hi(wm[i]);
+                }
+              }
+              mbar_arrive(bar(kBarBmFree + st));
+              ++cc;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) x[c2 * 32 + i] *= scale;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) x[i] *= scale;
+        }
+        if (ncols < kStepCols) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i >= ncols) x[i] = -INFINITY;
+        }
+
+        // ---- online softmax ----
+        float mx = x[0];
+#pragma unroll
+        for (int i = 1; i < 64; ++i) mx = fmaxf(mx, x[i]);
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = ex2f((m_run - m_use) * kLog2e);
+        const float ml2 = m_use * kLog2e;
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          x[i] = ex2f(fmaf(x[i], kLog2e, -ml2));
+          sum += x[i];
+        }
+        l_run = fmaf(l_run, alpha, sum);
+        m_run = m_new;
+
+        // ---- fold the previous step's P*V into the running output ----
+        if (s > 0) {
+          if (!mbar_wait(bar(kBarPvDone), pvc & 1u, ctx, 14)) return;
+          ++pvc;
+          tc_fence_after();
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_base + kTmemPV, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha_pend, __uint_as_float(r[i]));
+        }
+        alpha_pend = alpha;
+
+        // ---- hand P to the tensor core ----
+        if constexpr (kPTmem) {
+          uint32_t w[16];
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              w[i] = Elem<T>::pack(x[half * 32 + 2 * i], x[half * 32 + 2 * i + 1]);
+            tmem_st16(tmem + lane_base + kTmemP + (sh.pair ? hf * 32u : 0u) + half * 16u, w);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+        } else {
+          const uint32_t p_base = smem_base + p.off_p + (sh.pair ? hf * 16384u : 0u);
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w[i] = Elem<T>::pack(x[ch * 8 + 2 * i], x[ch * 8 + 2 * i + 1]);
+            sts128(p_base + sw128_offset(tid, ch), w);
+          }
+          fence_proxy_async_smem();
+          tc_fence_before();
+        }
+        mbar_arrive(bar(kBarPFull));
+      }
+
+      // ---- last P*V of the tile, then the epilogue ----
+      if (!mbar_wait(bar(kBarPvDone), pvc & 1u, ctx, 15)) return;
+      ++pvc;
+      tc_fence_after();
+      {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + kTmemPV, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha_pend, __uint_as_float(r[i]));
+      }
+      tc_fence_before();
+      if (row_ok) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint16_t* dst = static_cast<uint16_t*>(p.o) + bw * p.o_sbw + h * p.o_sh + row * p.o_sn;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 v;
+          v.x = Elem<T>::pack(acc[ch * 8 + 0] * inv, acc[ch * 8 + 1] * inv);
+          v.y = Elem<T>::pack(acc[ch * 8 + 2] * inv, acc[ch * 8 + 3] * inv);
+          v.z = Elem<T>::pack(acc[ch * 8 + 4] * inv, acc[ch * 8 + 5] * inv);
+          v.w = Elem<T>::pack(acc[ch * 8 + 6] * inv, acc[ch * 8 + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + ch * 8) = v;
+        }
+        const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+        p.lse[bw * p.lse_sbw + h * p.lse_sh + row] =
+            l_run > 0.f ? m_use + __logf(l_run) : -INFINITY;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// MMA issuer (one thread)
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool kPTmem>
+__device__ void fwd_mma_role(const FwdParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
+                             const WaitCtx& ctx) {
+  const FwdShape sh = fwd_shape(p);
+  constexpr uint32_t fmt = Elem<T>::kFmt;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const uint32_t nsb = sh.pair ? 1u : 2u;
+  const uint32_t idesc_pv = make_idesc(fmt, 128, 32, 0, 1);
+  uint32_t jt = 0, tt = 0, sc = 0, pc = 0;
+
+  for (int job = blockIdx.x; job < p.n_jobs; job += gridDim.x, ++jt) {
+    const uint32_t kvs = jt % p.n_kv_stages;
+    const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
+    const uint32_t v_base = k_base + static_cast<uint32_t>(sh.rows_kv) * kRowBytes;
+    if (!mbar_wait(bar(kBarKvReady + kvs), (jt / p.n_kv_stages) & 1u, ctx, 20)) return;
+
+    for (int mt = 0; mt < sh.MT; ++mt, ++tt) {
+      const uint32_t qs = tt & 1u;
+      const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
+      if (!mbar_wait(bar(kBarQReady + qs), (tt >> 1) & 1u, ctx, 21)) return;
+      tc_fence_after();
+
+      auto issue_scores = [&](int s) -> bool {
+        const uint32_t sb = sc % nsb;
+        if (!mbar_wait(bar(kBarSFree + sb), ((sc / nsb) & 1u) ^ 1u, ctx, 22)) return false;
+        tc_fence_after();
+        int ncols;
+        uint32_t kb, dcol;
+        if (sh.pair) {
+          ncols = 128;
+          kb = k_base;
+          dcol = kTmemS;
+        } else {
+          ncols = min(kStepCols, ((sh.N - s * kStepCols + 15) / 16) * 16);
+          kb = k_base + static_cast<uint32_t>(s) * kStepCols * kRowBytes;
+          dcol = kTmemS + sb * 64u;
+        }
+        const uint32_t idesc = make_idesc(fmt, 128, static_cast<uint32_t>(ncols), 0, 0);
+#pragma unroll
+        for (uint32_t k = 0; k < 2; ++k) {
+          mma_ss(tmem + dcol, make_smem_desc(q_base + k * 32u, 16, 512, kSw64),
+                 make_smem_desc(kb + k * 32u, 16, 512, kSw64), idesc, k);
+        }
+        mma_commit(bar(kBarSFull + sb));
+        ++sc;
+        return true;
+      };
+
+      if (!issue_scores(0)) return;
+      for (int s = 0; s < sh.KS; ++s, ++pc) {
+        if (s + 1 < sh.KS) {
+          if (!issue_scores(s + 1)) return;
+        }
+        if (s + 1 == sh.KS) mma_commit(bar(kBarQFree + qs));
+        if (!mbar_wait(bar(kBarPFull), pc & 1u, ctx, 23)) return;
+        tc_fence_after();
+        const uint32_t vb = sh.pair ? v_base : v_base + static_cast<uint32_t>(s) * kStepCols * kRowBytes;
+        const uint32_t ksteps = sh.pair ? 8u : 4u;
+        for (uint32_t k = 0; k < ksteps; ++k) {
+          const uint64_t bd = make_smem_desc(vb + k * 1024u, 512, 512, kSw64);
+          if constexpr (kPTmem) {
+            mma_ts(tmem + kTmemPV, tmem + kTmemP + k * 8u, bd, idesc_pv, k);
+          } else {
+            const uint32_t pa = smem_base + p.off_p + (k >> 2) * 16384u + (k & 3u) * 32u;
+            mma_ss(tmem + kTmemPV, make_smem_desc(pa, 16, 1024, kSw128), bd, idesc_pv, k);
+          }
+        }
+        mma_commit(bar(kBarPvDone));
+      }
+    }
+    mma_commit(bar(kBarKvFree + kvs));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// TMA producer (one thread).  Two independent streams are interleaved without ever blocking on
+// one of them: (a) K/V of a job and the Q tiles of its 128-row tiles, which run ahead by a whole
+// job when two K/V stages fit, and (b) the bias / mask table chunks, which stay a few chunks
+// ahead of the softmax warps.
+// ------------------------------------------------------------------------------------------------
+__device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t bars,
+                              const WaitCtx& ctx) {
+  const FwdShape sh = fwd_shape(p);
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const bool any_table = p.has_bias || p.has_mask;
+  const uint32_t table_bytes =
+      (p.has_bias ? kTableTileBytes : 0u) + (p.has_mask ? kTableTileBytes : 0u);
+
+  // stream (a): item 0 of a job is K/V, items 1..MT are the Q tiles
+  int a_job = blockIdx.x, a_item = 0;
+  uint32_t a_jt = 0, a_tt = 0;
+  // stream (b)
+  int b_job = blockIdx.x, b_mt = 0, b_s = 0, b_c2 = 0;
+  uint32_t b_cc = 0;
+  bool a_done = a_job >= p.n_jobs;
+  bool b_done = !any_table || b_job >= p.n_jobs;
+
+  long long t0 = clock64();
+  uint32_t idle = 0;
+  while (!a_done || !b_done) {
+    bool progress = false;
+    if (!a_done) {
+      if (a_item == 0) {
+        const uint32_t kvs = a_jt % p.n_kv_stages;
+        if (mbar_try_wait(bar(kBarKvFree + kvs), ((a_jt / p.n_kv_stages) & 1u) ^ 1u)) {
+          const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
+          const uint32_t v_base = k_base + static_cast<uint32_t>(sh.rows_kv) * kRowBytes;
+          const uint32_t full = bar(kBarKvFull + kvs);
+          mbar_arrive_expect_tx(full, 2u * static_cast<uint32_t>(sh.rows_kv) * kRowBytes);
+          const int nbox = sh.rows_kv / kBoxRows;
+          for (int b = 0; b < nbox; ++b) {
+            int bw, h, r0;
+            if (sh.pair) {
+              const int unit = 2 * a_job + b;
+              bw = unit / sh.H; h = unit - bw * sh.H; r0 = 0;
+            } else {
+              bw = a_job / sh.H; h = a_job - bw * sh.H; r0 = b * kBoxRows;
+            }
+            tma_load_4d(k_base + b * kBoxBytes, &p.tm_k, full, 0, r0, h, bw);
+            tma_load_4d(v_base + b * kBoxBytes, &p.tm_v, full, 0, r0, h, bw);
+          }
+          a_item = 1;
+          progress = true;
+        }
+      } else {
+        const uint32_t qs = a_tt & 1u;
+        if (mbar_try_wait(bar(kBarQFree + qs), ((a_tt >> 1) & 1u) ^ 1u)) {
+          const int mt = a_item - 1;
+          const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
+          const uint32_t qfull = bar(kBarQFull + qs);
+          mbar_arrive_expect_tx(qfull, 2u * kBoxBytes);
+          for (int b = 0; b < 2; ++b) {
+            int bw, h, r0;
+            if (sh.pair) {
+              const int unit = 2 * a_job + b;
+              bw = unit / sh.H; h = unit - bw * sh.H; r0 = 0;
+            } else {
+              bw = a_job / sh.H; h = a_job - bw * sh.H; r0 = mt * kTileRows + b * kBoxRows;
+            }
+            tma_load_4d(q_base + b * kBoxBytes, &p.tm_q, qfull, 0, r0, h, bw);
+          }
+          ++a_tt;
+          if (++a_item > sh.MT) {
+            a_item = 0;
+            ++a_jt;
+            a_job += gridDim.x;
+            a_done = a_job >= p.n_jobs;
+          }
+          progress = true;
+        }
+      }
+    }
+    if (!b_done) {
+      const uint32_t st = b_cc % p.n_bm_stages;
+      if (mbar_try_wait(bar(kBarBmFree + st), ((b_cc / p.n_bm_stages) & 1u) ^ 1u)) {
+        const uint32_t base = smem_base + p.off_bm + st * (2u * kTableTileBytes);
+        const uint32_t full = bar(kBarBmFull + st);
+        mbar_arrive_expect_tx(full, table_bytes);
+        for (int b = 0; b < 2; ++b) {
+          int bw, h, r0, c0;
+          if (sh.pair) {
+            const int unit = 2 * b_job + b;
+            bw = unit / sh.H; h = unit - bw * sh.H; r0 = 0; c0 = b_c2 * kChunkCols;
+          } else {
+            bw = b_job / sh.H; h = b_job - bw * sh.H;
+            r0 = b_mt * kTileRows + b * kBoxRows;
+            c0 = b_s * kStepCols + b_c2 * kChunkCols;
+          }
+          if (p.has_bias) tma_load_3d(base + b * kBoxBytes, &p.tm_bias, full, c0, r0, h);
+          if (p.has_mask)
+            tma_load_3d(base + kTableTileBytes + b * kBoxBytes, &p.tm_mask, full, c0, r0, bw % p.nW);
+        }
+        ++b_cc;
+        // advance (chunk, step, tile, job)
+        const int ncols = sh.pair ? sh.N : min(kStepCols, sh.N - b_s * kStepCols);
+        const int nch = ncols > kChunkCols ? 2 : 1;
+        if (++b_c2 >= nch) {
+          b_c2 = 0;
+          if (++b_s >= sh.KS) {
+            b_s = 0;
+            if (++b_mt >= sh.MT) {
+              b_mt = 0;
+              b_job += gridDim.x;
+              b_done = b_job >= p.n_jobs;
+            }
+          }
+        }
+        progress = true;
+      }
+    }
+    if (progress) {
+      idle = 0;
+    } else if ((++idle & 0x3Fu) == 0) {
+      if (idle == 0x40u) t0 = clock64();
+      if (*ctx.abort_flag) return;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *ctx.abort_flag = 1u;
+        if (ctx.status != nullptr) {
+          if (atomicCAS(&ctx.status->code, 0u, (30u << 8) | kStatusTimeout) == 0u) {
+            ctx.status->block = blockIdx.x;
+            ctx.status->detail = (static_cast<uint32_t>(a_item) << 16) | (b_cc & 0xFFFFu);
+          }
+        }
+        return;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool kPTmem>
+__global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_constant__ FwdParams p) {
+  // No static shared memory: the dynamic window then starts 1024-byte aligned, which the
+  // swizzled tiles need; checked below.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t tid = threadIdx.x;
+  const uint32_t warp = tid >> 5;
+  const uint32_t lane = tid & 31u;
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const uint32_t bars = smem_base + p.off_ctrl;
+  uint32_t* ctrl_words = reinterpret_cast<uint32_t*>(smem_raw + p.off_ctrl + 8u * kFwdNumBars);
+  uint32_t& tmem_slot = ctrl_words[0];
+  volatile uint32_t& abort_flag = *reinterpret_cast<volatile uint32_t*>(&ctrl_words[1]);
+  if ((smem_base & 1023u) != 0u) {
+    if (tid == 0 && p.status != nullptr) atomicCAS(&p.status->code, 0u, (99u << 8) | 2u);
+    return;
+  }
+
+  if (tid == 0) {
+    abort_flag = 0u;
+    for (int i = 0; i < kFwdNumBars; ++i) {
+      uint32_t count = 1u;
+      if ((i >= kBarKvReady && i < kBarKvFree) || (i >= kBarQReady && i < kBarQFree) ||
+          (i >= kBarSFree && i < kBarBmFull) || (i >= kBarBmFree && i < kBarPFull) || i == kBarPFull)
+        count = 128u;
+      mbar_init(bars + 8u * i, count);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&p.tm_q);
+    tma_prefetch_desc(&p.tm_k);
+    tma_prefetch_desc(&p.tm_v);
+    if (p.has_bias) tma_prefetch_desc(&p.tm_bias);
+    if (p.has_mask) tma_prefetch_desc(&p.tm_mask);
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&tmem_slot), kFwdTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  WaitCtx ctx{&ctrl_words[1], p.status};
+
+  if (warp < 4) {
+    fwd_softmax_role<T, kPTmem>(p, smem_base, bars, tmem, ctx);
+  } else if (lane == 0) {
+    if (warp == 4) fwd_mma_role<T, kPTmem>(p, smem_base, bars, tmem, ctx);
+    else fwd_load_role(p, smem_base, bars, ctx);
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    // A wait ran out somewhere: give copies that may still be in flight time to land before the
+    // shared memory is handed back.
+    __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 4) tmem_dealloc(tmem, kFwdTmemCols);
+}
+
+template __global__ void fwd_kernel<__nv_bfloat16, true>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__nv_bfloat16, false>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__half, true>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__half, false>(const __grid_constant__ FwdParams);
+
+cudaError_t launch_fwd(const FwdParams& p, int dtype_is_bf16, int p_in_tmem, int grid,
+                       cudaStream_t stream) {
+  auto go = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(p.smem_bytes));
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kFwdThreads, p.smem_bytes, stream>>>(p);
+    return cudaGetLastError();
+  };
+  if (dtype_is_bf16) {
+    return p_in_tmem ? go(fwd_kernel<__nv_bfloat16, true>) : go(fwd_kernel<__nv_bfloat16, false>);
+  }
+  return p_in_tmem ? go(fwd_kernel<__half, true>) : go(fwd_kernel<__half, false>);
+}
+
+}  // namespace fwa2

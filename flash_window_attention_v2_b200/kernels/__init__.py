@@ -1,0 +1,147 @@
+"""Drop-in replacement for the reference package `flash_win_attn_v2.kernels`.
+
+Exports the same two names with the same signatures, argument meaning and
+assertion behaviour (flash_win_attn_v2/kernels/__init__.py:1-2):
+
+* `_flash_attn_forward`  (attn_kernel_forward.py:261-345)
+* `_flash_attn_backward` (attn_kernel_backward.py:567-711)
+
+Both marshal raw device pointers into the C ABI of libfwa2_b200.so (hand-written
+sm_100a kernels).  PyTorch is used only for device memory and the current
+stream.  There is no Triton, no alternative backend and no CPU path: without
+the compiled library, or on a failure inside it, these functions raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import _lib
+
+__all__ = ["_flash_attn_forward", "_flash_attn_backward", "check_device_status"]
+
+_DTYPES = {torch.float16: _lib.FWA2_F16, torch.bfloat16: _lib.FWA2_BF16}
+_status_words: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status_words.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=device)
+        _status_words[idx] = t
+    return t
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if a kernel recorded a device-side timeout."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    torch.cuda.synchronize(device)
+    st = _status(device).cpu().tolist()
+    if st[0] != 0:
+        _status(device).zero_()
+        raise RuntimeError(f"fwa2 device status: site {st[0] >> 8}, kind {st[0] & 255}, "
+                           f"block {st[1]}, detail {st[2]}")
+
+
+def _t4(x: torch.Tensor) -> _lib.Tensor4:
+    return _lib.Tensor4(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2))
+
+
+def _tma_ok(x: torch.Tensor) -> bool:
+    """Inner stride 1, every other stride a multiple of 8 elements, 16-byte aligned base."""
+    if x.stride(-1) != 1 or x.data_ptr() % 16 != 0:
+        return False
+    return all(x.shape[i] == 1 or (x.stride(i) > 0 and x.stride(i) % 8 == 0) for i in range(3))
+
+
+def _rows(x: torch.Tensor) -> torch.Tensor:
+    return x if _tma_ok(x) else x.contiguous()
+
+
+def _table(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """A (planes, N, N) table with a row pitch TMA can address (multiple of 8 elements)."""
+    if t.dtype != dtype:
+        t = t.to(dtype)
+    n = t.shape[-1]
+    if n % 8 != 0:
+        t = torch.nn.functional.pad(t, (0, 8 - n % 8))
+    elif not t.is_contiguous():
+        t = t.contiguous()
+    return t
+
+
+def _stream(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="scalar",
+                        _variant: int = 0, _max_ctas: int = 0):
+    batch_window_size, n_heads, seqlen_q, d = q.shape
+    _, _, seqlen_k, _ = k.shape
+    assert k.shape == (batch_window_size, n_heads, seqlen_k, d)
+    assert v.shape == (batch_window_size, n_heads, seqlen_k, d)
+    assert d <= 128, "FlashAttention only support head dimensions up to 128"
+    assert q.dtype == k.dtype == v.dtype, "All tensors must have the same type"
+    assert q.dtype in [torch.float16, torch.bfloat16], "Only support fp16 and bf16"
+    assert q.is_cuda and k.is_cuda and v.is_cuda and logit_scale.is_cuda
+    assert seqlen_q == seqlen_k, "window attention is self-attention: seqlen_q must equal seqlen_k"
+    if scale_type == "tensor":
+        assert logit_scale.shape == (n_heads, 1, 1)
+        assert logit_scale.dtype == q.dtype
+        if not logit_scale.is_contiguous():
+            logit_scale = logit_scale.contiguous()
+    else:
+        assert logit_scale.dtype == torch.float32 and logit_scale.numel() == 1
+    if bias is not None:
+        assert bias.dtype == q.dtype
+        assert bias.is_cuda
+        assert bias.shape == (n_heads, seqlen_q, seqlen_k)
+    n_windows = 0
+    if mask is not None:
+        assert mask.dtype in [q.dtype, torch.float]
+        assert mask.is_cuda
+        assert mask.shape[1:] == (seqlen_q, seqlen_k)
+        n_windows = mask.shape[0]
+        assert batch_window_size % n_windows == 0
+
+    seqlen_q_rounded = math.ceil(seqlen_q / 64) * 64
+    lse = torch.empty((batch_window_size, n_heads, seqlen_q_rounded), device=q.device, dtype=torch.float32)
+    o = torch.empty_like(q)
+    if not _tma_ok(o):
+        o = torch.empty(q.shape, device=q.device, dtype=q.dtype)
+
+    qc, kc, vc = _rows(q), _rows(k), _rows(v)
+    bias_t = _table(bias, q.dtype) if bias is not None else None
+    mask_t = _table(mask, q.dtype) if mask is not None else None
+
+    a = _lib.FwdArgs()
+    a.struct_size = C.sizeof(_lib.FwdArgs)
+    a.abi_version = _lib.FWA2_ABI_VERSION
+    a.dtype = _DTYPES[q.dtype]
+    a.bw, a.heads, a.n, a.head_dim = batch_window_size, n_heads, seqlen_q, d
+    a.n_windows = n_windows
+    a.q, a.k, a.v, a.o = _t4(qc), _t4(kc), _t4(vc), _t4(o)
+    a.lse = lse.data_ptr()
+    a.lse_stride_bw, a.lse_stride_h = lse.stride(0), lse.stride(1)
+    a.logit_scale = logit_scale.data_ptr()
+    a.scale_is_tensor = 1 if scale_type == "tensor" else 0
+    a.bias = bias_t.data_ptr() if bias_t is not None else None
+    a.mask = mask_t.data_ptr() if mask_t is not None else None
+    a.bias_row_stride = bias_t.stride(1) if bias_t is not None else 0
+    a.mask_row_stride = mask_t.stride(1) if mask_t is not None else 0
+    a.status = _status(q.device).data_ptr()
+    a.variant = _variant
+    a.max_ctas = _max_ctas
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().fwa2_forward(C.byref(a), _stream(q.device)), "fwa2_forward")
+    return o, lse, logit_scale
+
+
+def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, db,
+                         bias=None, mask=None, scale_type="scalar", _partial_out=None,
+                         _variant: int = 0, _max_ctas: int = 0):
+    raise NotImplementedError("backward kernel not built yet")

@@ -1,0 +1,130 @@
+/* C ABI of the B200 window-attention library (libfwa2_b200.so).
+ *
+ * Plain pointers and sizes only; no torch types.  Every device buffer, including the
+ * workspace, is owned by the caller; the library allocates no device memory and keeps no
+ * mutable global state.  All entry points return 0 on success and a negative code on error
+ * (see fwa2_strerror); nothing is launched when an argument check fails.  No entry point
+ * synchronises the host with the device, so calls may be captured in a CUDA graph.
+ *
+ * The two compute entry points are what a binding for the reference project's kernel package
+ * (flash_win_attn_v2/kernels/__init__.py:1-2) calls in place of its Triton launches.
+ */
+#ifndef FWA2_H_
+#define FWA2_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FWA2_ABI_VERSION 1
+
+enum fwa2_dtype { FWA2_F16 = 0, FWA2_BF16 = 1 };
+
+enum fwa2_error {
+  FWA2_OK = 0,
+  FWA2_ERR_NULL = -1,          /* a required pointer is null */
+  FWA2_ERR_DTYPE = -2,         /* dtype is not f16 / bf16 */
+  FWA2_ERR_HEAD_DIM = -3,      /* head dimension other than 32 */
+  FWA2_ERR_SHAPE = -4,         /* non-positive size, N > 640, BW not a multiple of nW, ... */
+  FWA2_ERR_STRIDE = -5,        /* a stride that TMA cannot express (not a multiple of 8 elements) */
+  FWA2_ERR_ALIGN = -6,         /* a base pointer that is not 16-byte aligned */
+  FWA2_ERR_WORKSPACE = -7,     /* workspace missing or too small */
+  FWA2_ERR_DRIVER = -8,        /* the CUDA driver entry point for tensor maps is unavailable */
+  FWA2_ERR_TENSOR_MAP = -9,    /* cuTensorMapEncodeTiled rejected a descriptor */
+  FWA2_ERR_ABI = -10,          /* struct_size / abi_version mismatch */
+  FWA2_ERR_LAUNCH = -11        /* the CUDA runtime refused the launch (see fwa2_last_cuda_error) */
+};
+
+/* A (BW, H, N, 32) tensor of 16-bit elements with unit stride along the last axis.
+ * Strides are in elements. */
+typedef struct fwa2_tensor4 {
+  void* ptr;
+  int64_t stride_bw, stride_h, stride_n;
+} fwa2_tensor4;
+
+/* Arguments of the forward pass.
+ * Replaces `_flash_attn_forward` (flash_win_attn_v2/kernels/attn_kernel_forward.py:261-345). */
+typedef struct fwa2_fwd_args {
+  uint32_t struct_size;     /* sizeof(fwa2_fwd_args) */
+  uint32_t abi_version;     /* FWA2_ABI_VERSION */
+  int32_t dtype;            /* fwa2_dtype of q, k, v, o, bias, mask and (tensor mode) logit_scale */
+  int32_t bw, heads, n, head_dim;
+  int32_t n_windows;        /* mask.shape[0]; the mask of row b of BW is b mod n_windows; 0 if no mask */
+  fwa2_tensor4 q, k, v;     /* inputs */
+  fwa2_tensor4 o;           /* output, same dtype */
+  float* lse;               /* (BW, H, lse_stride_h) fp32: natural-log sum-exp per query row */
+  int64_t lse_stride_bw, lse_stride_h;
+  const void* logit_scale;  /* tensor mode: H values of `dtype` (the log-domain parameter);
+                               scalar mode: one fp32 multiplier */
+  int32_t scale_is_tensor;  /* 1 = tensor mode: scale_h = exp(min(g_h, ln 100)) */
+  const void* bias;         /* (H, N, bias_row_stride) or NULL */
+  const void* mask;         /* (n_windows, N, mask_row_stride) or NULL */
+  int64_t bias_row_stride, mask_row_stride;  /* elements; multiples of 8 */
+  void* status;             /* optional 16-byte device word block written only on a device-side
+                               timeout (must be zero-initialised by the caller); may be NULL */
+  int32_t variant;          /* 0 = default; 1 = keep P in shared memory instead of tensor memory */
+  int32_t max_ctas;         /* 0 = default (fill the device); otherwise an upper bound on the grid */
+} fwa2_fwd_args;
+
+/* Arguments of the backward pass.
+ * Replaces `_flash_attn_backward` (flash_win_attn_v2/kernels/attn_kernel_backward.py:567-711),
+ * including its delta pre-pass (:6-51), the fp32 accumulators and the final casts (:703-711). */
+typedef struct fwa2_bwd_args {
+  uint32_t struct_size;
+  uint32_t abi_version;
+  int32_t dtype;
+  int32_t bw, heads, n, head_dim;
+  int32_t n_windows;
+  fwa2_tensor4 q, k, v, o, dout;      /* inputs */
+  fwa2_tensor4 dq, dk, dv;            /* outputs, fully overwritten */
+  const float* lse;
+  int64_t lse_stride_bw, lse_stride_h;
+  const void* logit_scale;
+  int32_t scale_is_tensor;
+  const void* bias;
+  const void* mask;
+  int64_t bias_row_stride, mask_row_stride;
+  void* dbias;              /* (H, N, N) contiguous, `dtype`; NULL when there is no bias */
+  void* dscale;             /* H values of `dtype`; NULL in scalar mode */
+  float* partial_out;       /* optional (H*N*N + H) fp32: if non-NULL the window-summed dBias and
+                               dLogitScale are written here in fp32 (before the clamp gate and
+                               the cast) and dbias / dscale are left untouched, so that several
+                               GPUs can sum their shards before fwa2_finalize_grads */
+  void* workspace;          /* at least fwa2_bwd_workspace_bytes() bytes, 256-byte aligned */
+  size_t workspace_bytes;
+  void* status;
+  int32_t variant;
+  int32_t max_ctas;
+} fwa2_bwd_args;
+
+int fwa2_abi_version(void);
+const char* fwa2_strerror(int code);
+/* cudaError_t value of the most recent failed runtime / driver call on this thread (0 if none). */
+int fwa2_last_cuda_error(void);
+
+/* Forward pass on `stream` (a cudaStream_t). */
+int fwa2_forward(const fwa2_fwd_args* args, void* stream);
+
+/* Scratch bytes the backward pass needs for the given problem (0 on invalid sizes). */
+size_t fwa2_bwd_workspace_bytes(int32_t bw, int32_t heads, int32_t n, int32_t n_windows,
+                                int32_t has_bias, int32_t has_mask);
+/* Backward pass on `stream`. */
+int fwa2_backward(const fwa2_bwd_args* args, void* stream);
+
+/* Cast a (possibly all-reduced) fp32 partial buffer [H*N*N dBias | H dLogitScale] to the output
+ * dtype; dLogitScale is multiplied by 1[g_h <= ln 100] first
+ * (attn_kernel_backward.py:703-711).  dbias / dscale may be NULL. */
+int fwa2_finalize_grads(const float* partial, int32_t dtype, int32_t heads, int32_t n,
+                        const void* logit_scale, void* dbias, void* dscale, void* stream);
+
+/* Device self-checks of the tensor-core building blocks (used by the test-suite). */
+int fwa2_selftest_mma(int mode, int dtype, const void* a, const void* b, float* d, void* status,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FWA2_H_ */
