@@ -12,6 +12,13 @@ namespace fwa2 {
 
 cudaError_t launch_fwd(const FwdParams& p, int dtype_is_bf16, int p_in_tmem, int grid,
                        cudaStream_t stream);
+cudaError_t launch_bwd(const BwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
+cudaError_t launch_transpose_tables(const void* bias, long long bias_pitch, void* bias_t,
+                                    const void* mask, long long mask_pitch, void* mask_t, int n_bias,
+                                    int n_mask, int n, int dst_pitch, cudaStream_t stream);
+cudaError_t launch_reduce_partials(const ReduceParams& p, int dtype_is_bf16, cudaStream_t stream);
+cudaError_t launch_finalize(const float* partial, int dtype_is_bf16, int H, int N,
+                            const void* logit_scale, void* dbias, void* dscale, cudaStream_t stream);
 
 namespace {
 
@@ -125,6 +132,38 @@ int check_common(int dtype, int bw, int heads, int n, int head_dim, int n_window
 
 constexpr uint32_t kCtrlBytes = 512;
 
+size_t align256(size_t x) { return (x + 255u) & ~static_cast<size_t>(255u); }
+
+// How the backward pass carves up its workspace and its grid.
+struct BwdPlan {
+  int pair, nslots, grid, n_bufs, table_pitch, db_pitch;
+  size_t off_bias_t, off_mask_t, off_db, off_dscale, total;
+};
+
+BwdPlan make_bwd_plan(int bw, int heads, int n, int n_windows, bool has_bias, bool has_mask,
+                      int sm_count) {
+  BwdPlan pl;
+  pl.pair = n <= 64;
+  const int per_head = sm_count / heads > 0 ? sm_count / heads : 1;
+  const int jobs = pl.pair ? (bw + 1) / 2 : bw;
+  pl.nslots = per_head < jobs ? per_head : jobs;
+  pl.grid = pl.nslots * heads;
+  pl.n_bufs = pl.grid * (pl.pair ? 2 : 1);
+  pl.table_pitch = ((n + 7) / 8) * 8;
+  pl.db_pitch = ((n + 31) / 32) * 32;
+  size_t off = 0;
+  pl.off_bias_t = off;
+  if (has_bias) off += align256(static_cast<size_t>(heads) * n * pl.table_pitch * 2u);
+  pl.off_mask_t = off;
+  if (has_mask) off += align256(static_cast<size_t>(n_windows) * n * pl.table_pitch * 2u);
+  pl.off_db = off;
+  if (has_bias) off += align256(static_cast<size_t>(pl.n_bufs) * n * pl.db_pitch * 4u);
+  pl.off_dscale = off;
+  off += align256(static_cast<size_t>(pl.grid) * 4u);
+  pl.total = off;
+  return pl;
+}
+
 }  // namespace
 }  // namespace fwa2
 
@@ -229,5 +268,145 @@ extern "C" int fwa2_forward(const fwa2_fwd_args* a, void* stream) {
     g_last_cuda_error = static_cast<int>(e);
     return FWA2_ERR_LAUNCH;
   }
+  return FWA2_OK;
+}
+
+extern "C" size_t fwa2_bwd_workspace_bytes(int32_t bw, int32_t heads, int32_t n, int32_t n_windows,
+                                           int32_t has_bias, int32_t has_mask) {
+  if (bw <= 0 || heads <= 0 || n <= 0 || n > 640 || (has_mask && n_windows <= 0)) return 0;
+  const DeviceInfo dev = device_info();
+  const int sms = dev.ok ? dev.sm_count : 148;
+  return make_bwd_plan(bw, heads, n, n_windows, has_bias != 0, has_mask != 0, sms).total;
+}
+
+extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
+  if (a == nullptr) return FWA2_ERR_NULL;
+  if (a->struct_size != sizeof(fwa2_bwd_args) || a->abi_version != FWA2_ABI_VERSION) return FWA2_ERR_ABI;
+  const bool has_bias = a->bias != nullptr, has_mask = a->mask != nullptr;
+  int rc = check_common(a->dtype, a->bw, a->heads, a->n, a->head_dim, a->n_windows, has_mask);
+  if (rc != FWA2_OK) return rc;
+  if (a->lse == nullptr || a->logit_scale == nullptr) return FWA2_ERR_NULL;
+  const fwa2_tensor4* plain[] = {&a->q, &a->k, &a->o, &a->dq, &a->dk, &a->dv};
+  for (const fwa2_tensor4* t : plain) {
+    if (t->ptr == nullptr) return FWA2_ERR_NULL;
+    if (!aligned16(t->ptr)) return FWA2_ERR_ALIGN;
+    if ((t->stride_n % 8) != 0 || (t->stride_h % 8) != 0 || (t->stride_bw % 8) != 0) return FWA2_ERR_STRIDE;
+  }
+  if (has_bias && a->dbias == nullptr && a->partial_out == nullptr) return FWA2_ERR_NULL;
+  if (has_bias && (a->bias_row_stride < a->n)) return FWA2_ERR_STRIDE;
+  if (has_mask && (a->mask_row_stride < a->n)) return FWA2_ERR_STRIDE;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  const DeviceInfo dev = device_info();
+  if (!dev.ok) return FWA2_ERR_LAUNCH;
+  BwdPlan pl = make_bwd_plan(a->bw, a->heads, a->n, a->n_windows, has_bias, has_mask, dev.sm_count);
+  if (a->max_ctas > 0 && pl.grid > a->max_ctas) {
+    // a smaller grid keeps the same workspace layout (it only uses a prefix of it)
+    int ns = a->max_ctas / a->heads;
+    if (ns < 1) ns = 1;
+    if (ns < pl.nslots) { pl.nslots = ns; pl.grid = ns * a->heads; }
+  }
+  if (a->workspace == nullptr || a->workspace_bytes < pl.total ||
+      (reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0)
+    return FWA2_ERR_WORKSPACE;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  void* bias_t = ws + pl.off_bias_t;
+  void* mask_t = ws + pl.off_mask_t;
+
+  cudaError_t e = launch_transpose_tables(a->bias, a->bias_row_stride, bias_t, a->mask,
+                                          a->mask_row_stride, mask_t, has_bias ? a->heads : 0,
+                                          has_mask ? a->n_windows : 0, a->n, pl.table_pitch, stream);
+  if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
+
+  BwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  if ((rc = encode_rows4(&p.tm_q, a->q, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+  if ((rc = encode_rows4(&p.tm_k, a->k, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+  if ((rc = encode_rows4(&p.tm_v, a->v, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+  if ((rc = encode_rows4(&p.tm_do, a->dout, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+  if (has_bias &&
+      (rc = encode_table3(&p.tm_biasT, bias_t, a->dtype, a->heads, a->n, a->n, pl.table_pitch)) != FWA2_OK)
+    return rc;
+  if (has_mask &&
+      (rc = encode_table3(&p.tm_maskT, mask_t, a->dtype, a->n_windows, a->n, a->n, pl.table_pitch)) != FWA2_OK)
+    return rc;
+
+  p.q = a->q.ptr; p.q_sbw = a->q.stride_bw; p.q_sh = a->q.stride_h; p.q_sn = a->q.stride_n;
+  p.k = a->k.ptr; p.k_sbw = a->k.stride_bw; p.k_sh = a->k.stride_h; p.k_sn = a->k.stride_n;
+  p.o = a->o.ptr; p.o_sbw = a->o.stride_bw; p.o_sh = a->o.stride_h; p.o_sn = a->o.stride_n;
+  p.dq = a->dq.ptr; p.dq_sbw = a->dq.stride_bw; p.dq_sh = a->dq.stride_h; p.dq_sn = a->dq.stride_n;
+  p.dk = a->dk.ptr; p.dk_sbw = a->dk.stride_bw; p.dk_sh = a->dk.stride_h; p.dk_sn = a->dk.stride_n;
+  p.dv = a->dv.ptr; p.dv_sbw = a->dv.stride_bw; p.dv_sh = a->dv.stride_h; p.dv_sn = a->dv.stride_n;
+  p.lse = a->lse; p.lse_sbw = a->lse_stride_bw; p.lse_sh = a->lse_stride_h;
+  p.scale = a->logit_scale; p.scale_is_tensor = a->scale_is_tensor;
+  p.db_partial = has_bias ? reinterpret_cast<float*>(ws + pl.off_db) : nullptr;
+  p.db_pitch = pl.db_pitch;
+  p.db_buf_stride = static_cast<long long>(a->n) * pl.db_pitch;
+  p.dscale_partial = reinterpret_cast<float*>(ws + pl.off_dscale);
+  p.BW = a->bw; p.H = a->heads; p.N = a->n; p.nW = has_mask ? a->n_windows : 1;
+  p.has_bias = has_bias; p.has_mask = has_mask;
+  p.pair_mode = pl.pair;
+  p.nslots = pl.nslots;
+  p.status = static_cast<DeviceStatus*>(a->status);
+
+  // ---- shared memory layout (one CTA per SM) ----
+  p.rows_kv = pl.pair ? 128 : ((a->n + 127) / 128) * 128;
+  p.kv_stage_bytes = 2u * static_cast<uint32_t>(p.rows_kv) * kRowBytes;
+  const uint32_t qdo_bytes = 3u * 4u * kBoxBytes;
+  const uint32_t bm_stage = 2u * kTableTileBytes;
+  const bool any_table = has_bias || has_mask;
+  auto total = [&](uint32_t nkv, uint32_t nds, uint32_t nbm) {
+    return nkv * p.kv_stage_bytes + qdo_bytes + nds * 32768u + (any_table ? 2u * nbm * bm_stage : 0u) +
+           nkv * static_cast<uint32_t>(p.rows_kv) * 4u + 3u * 1024u + kCtrlBytes;
+  };
+  const uint32_t budget = static_cast<uint32_t>(dev.max_smem_optin);
+  const uint32_t opts[][3] = {{2, 2, 2}, {2, 1, 2}, {1, 2, 2}, {1, 1, 2}, {1, 1, 1}};
+  uint32_t nkv = 0, nds = 0, nbm = 0;
+  for (const auto& o : opts) {
+    if (total(o[0], o[1], o[2]) <= budget) { nkv = o[0]; nds = o[1]; nbm = o[2]; break; }
+  }
+  if (nkv == 0) return FWA2_ERR_SHAPE;
+  p.n_kv_stages = static_cast<int>(nkv);
+  p.n_ds_bufs = static_cast<int>(nds);
+  p.n_bm_stages = static_cast<int>(nbm);
+  p.off_kv = 0;
+  p.off_qdo = p.off_kv + nkv * p.kv_stage_bytes;
+  p.off_ds = p.off_qdo + qdo_bytes;
+  p.off_bm = p.off_ds + nds * 32768u;
+  p.off_rk = p.off_bm + (any_table ? 2u * nbm * bm_stage : 0u);
+  p.off_rowstats = p.off_rk + nkv * static_cast<uint32_t>(p.rows_kv) * 4u;
+  p.off_ctrl = p.off_rowstats + 3u * 1024u;
+  p.smem_bytes = p.off_ctrl + kCtrlBytes;
+
+  e = launch_bwd(p, a->dtype == FWA2_BF16, pl.grid, stream);
+  if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
+
+  if (has_bias || a->scale_is_tensor) {
+    ReduceParams r;
+    std::memset(&r, 0, sizeof(r));
+    r.db_partial = p.db_partial;
+    r.buf_stride = p.db_buf_stride;
+    r.pitch = pl.db_pitch;
+    r.dscale_partial = a->scale_is_tensor ? p.dscale_partial : nullptr;
+    r.H = a->heads; r.N = a->n; r.BW = a->bw; r.nslots = pl.nslots; r.pair = pl.pair;
+    r.out_f32 = a->partial_out;
+    r.dbias = a->dbias;
+    r.dscale = a->dscale;
+    r.logit_scale = a->logit_scale;
+    e = launch_reduce_partials(r, a->dtype == FWA2_BF16, stream);
+    if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
+  }
+  return FWA2_OK;
+}
+
+extern "C" int fwa2_finalize_grads(const float* partial, int32_t dtype, int32_t heads, int32_t n,
+                                   const void* logit_scale, void* dbias, void* dscale, void* stream) {
+  if (partial == nullptr) return FWA2_ERR_NULL;
+  if (dtype != FWA2_F16 && dtype != FWA2_BF16) return FWA2_ERR_DTYPE;
+  if (heads <= 0 || heads > 256 || n <= 0) return FWA2_ERR_SHAPE;
+  if (dscale != nullptr && logit_scale == nullptr) return FWA2_ERR_NULL;
+  cudaError_t e = launch_finalize(partial, dtype == FWA2_BF16, heads, n, logit_scale, dbias, dscale,
+                                  static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
   return FWA2_OK;
 }

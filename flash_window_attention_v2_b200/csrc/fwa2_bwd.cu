@@ -1,6 +1,828 @@
-// Backward kernel (placeholder until the kernel lands): the entry points exist so that the
-// library exports its full ABI, and fail loudly.
-#include "../../include/fwa2.h"
+// Backward kernel: recomputes the scores and produces dQ, dK, dV (through the L2-normalisation
+// Jacobian), per-CTA partial sums of dBias and of dLogitScale, with no contended atomics.
+//
+// Everything is computed TRANSPOSED: S^T = K^ Q^^T and dP^T = V dO^T put keys on the 128 TMEM
+// lanes, so that P^T and dS^T (written back over S^T / dP^T as packed 16-bit pairs) are directly
+// the tensor-memory A operands of dV += P^T dO and dK^ += dS^T Q^.  Only dS takes a trip
+// through shared memory, as the A operand of dQ^ += dS K^.
+//
+// One persistent CTA per SM.  A tile is 128 keys x 128 queries; its two 64-query halves
+// ("steps") are processed concurrently by two warpgroups.  Roles:
+//   warps 0-3   warpgroup 0: thread t owns key t of the tile, queries [0, 64)
+//   warps 4-7   warpgroup 1: same keys, queries [64, 128)
+//   warp  8     issues every tcgen05.mma (one thread)
+//   warp  9     TMA producer (one thread)
+// Replaces flash_win_attn_v2/kernels/attn_kernel_backward.py:6-51 (delta pre-pass) and
+// :84-564 (`_bwd_kernel`).
+#include "fwa2_common.cuh"
 
-extern "C" size_t fwa2_bwd_workspace_bytes(int32_t, int32_t, int32_t, int32_t, int32_t, int32_t) { return 0; }
-extern "C" int fwa2_backward(const fwa2_bwd_args*, void*) { return FWA2_ERR_LAUNCH; }
+namespace fwa2 {
+
+constexpr int kBwdThreads = 320;
+constexpr uint32_t kBwdTmemCols = 512;
+constexpr uint32_t kTmST = 0;       // S^T of warpgroup w at 128 w (64 columns), P^T written over it
+constexpr uint32_t kTmDPT = 64;     // dP^T of warpgroup w at 128 w + 64, dS^T written over it
+constexpr uint32_t kTmDV = 256;     // 32 columns
+constexpr uint32_t kTmDK = 288;     // 32 columns
+constexpr uint32_t kTmDQ = 320;     // 32 columns per 128-query tile, at most 5 tiles
+constexpr uint32_t kQdoStageBytes = 4u * kBoxBytes;   // [Q tile | dO tile]
+constexpr uint32_t kDsTileBytes = 32768u;
+constexpr int kNumQdoStages = 3;
+
+enum BwdBar : int {
+  kbKvFull = 0, kbKvReady = 2, kbKvFree = 4,
+  kbQdoFull = 6, kbQdoReady = 9, kbQdoFree = 12,
+  kbStFull = 15, kbPtFull = 17,
+  kbBmFull = 19, kbBmFree = 23,       // index + 2 * warpgroup + stage
+  kbDsFree = 27,
+  kbDkvFull = 29, kbDkvFree = 30, kbDqFull = 31, kbDqFree = 32,
+  kBwdNumBars = 33
+};
+
+struct BwdGeom {
+  int N, H, pair, KB, MT, h, slot, nslots, count, njobs;
+};
+
+__device__ __forceinline__ BwdGeom bwd_geom(const BwdParams& p) {
+  BwdGeom g;
+  g.N = p.N;
+  g.H = p.H;
+  g.pair = p.pair_mode;
+  g.KB = g.pair ? 1 : (p.N + kTileRows - 1) / kTileRows;
+  g.MT = g.KB;
+  g.h = static_cast<int>(blockIdx.x) % p.H;
+  g.slot = static_cast<int>(blockIdx.x) / p.H;
+  g.nslots = p.nslots;
+  g.count = g.slot < p.BW ? (p.BW - g.slot + g.nslots - 1) / g.nslots : 0;
+  g.njobs = g.pair ? (g.count + 1) / 2 : g.count;
+  return g;
+}
+
+// Window (row of BW) of member m of job t; BW (out of range: TMA then delivers zeros) if absent.
+__device__ __forceinline__ int bwd_bw(const BwdParams& p, const BwdGeom& g, int t, int m) {
+  const int idx = g.pair ? 2 * t + m : t;
+  return idx < g.count ? g.slot + idx * g.nslots : p.BW;
+}
+
+struct TileIt {
+  int t, j, i;   // job, key block, query tile
+};
+__device__ __forceinline__ bool tile_next(const BwdGeom& g, TileIt& it) {
+  if (++it.i >= g.MT) {
+    it.i = 0;
+    if (++it.j >= g.KB) {
+      it.j = 0;
+      ++it.t;
+    }
+  }
+  return it.t < g.njobs;
+}
+// Queries of step w of query tile i that exist (<= 0: the step is skipped by every role).
+__device__ __forceinline__ int step_rows(const BwdGeom& g, int i, int w) {
+  return g.pair ? kStepCols : g.N - kTileRows * i - kStepCols * w;
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr));
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// One 32-query chunk of a step for one key (= one thread):
+//   p = exp2(x log2e - lse2),  ds = p (dP - delta),  x = scale * cos + bias + mask.
+// Produces the packed P^T / dS^T words and adds ds into this CTA's dBias^T partial.
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool kRagged>
+__device__ __forceinline__ void bwd_chunk(bool has_bias, bool has_mask, const uint32_t (&sv)[32],
+                                          const uint32_t (&dpv)[32], uint32_t bias_tile,
+                                          uint32_t mask_tile, uint32_t lt, const float* lse2,
+                                          const float* delta, float scale, int rows_left,
+                                          float* db_ptr, bool db_store, uint32_t (&pw)[16],
+                                          uint32_t (&dw)[16]) {
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
+    if (has_bias) lds128(bias_tile + sw64_offset(lt, ch), wb);
+    if (has_mask) lds128(mask_tile + sw64_offset(lt, ch), wm);
+    const float4 la = *reinterpret_cast<const float4*>(lse2 + ch * 8);
+    const float4 lb = *reinterpret_cast<const float4*>(lse2 + ch * 8 + 4);
+    const float4 da = *reinterpret_cast<const float4*>(delta + ch * 8);
+    const float4 db = *reinterpret_cast<const float4*>(delta + ch * 8 + 4);
+    const float l8[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+    const float d8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+    float dsv[8];
+#pragma unroll
+    for (int e2 = 0; e2 < 4; ++e2) {
+      const int e = 2 * e2, idx = ch * 8 + e;
+      const float x0 = fmaf(__uint_as_float(sv[idx]), scale, Elem<T>::lo(wb[e2])) + Elem<T>::lo(wm[e2]);
+      const float x1 = fmaf(__uint_as_float(sv[idx + 1]), scale, Elem<T>::hi(wb[e2])) + Elem<T>::hi(wm[e2]);
+      float p0 = ex2f(fmaf(x0, kLog2e, -l8[e]));
+      float p1 = ex2f(fmaf(x1, kLog2e, -l8[e + 1]));
+      float s0 = p0 * (__uint_as_float(dpv[idx]) - d8[e]);
+      float s1 = p1 * (__uint_as_float(dpv[idx + 1]) - d8[e + 1]);
+      if (kRagged) {
+        // queries past the end of the window: the accumulator columns were never written
+        if (idx >= rows_left) { p0 = 0.f; s0 = 0.f; }
+        if (idx + 1 >= rows_left) { p1 = 0.f; s1 = 0.f; }
+      }
+      pw[ch * 4 + e2] = Elem<T>::pack(p0, p1);
+      dw[ch * 4 + e2] = Elem<T>::pack(s0, s1);
+      dsv[e] = s0;
+      dsv[e + 1] = s1;
+    }
+    if (db_ptr != nullptr) {
+      float* dst = db_ptr + ch * 8;
+      if (db_store) {
+        *reinterpret_cast<float4*>(dst) = make_float4(dsv[0], dsv[1], dsv[2], dsv[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(dsv[4], dsv[5], dsv[6], dsv[7]);
+      } else {
+        red_add_v4(dst, dsv[0], dsv[1], dsv[2], dsv[3]);
+        red_add_v4(dst + 4, dsv[4], dsv[5], dsv[6], dsv[7]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The two compute warpgroups
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t smem_base,
+                                 uint32_t bars, uint32_t tmem, const WaitCtx& ctx,
+                                 float& dscale_acc) {
+  const BwdGeom g = bwd_geom(p);
+  if (g.njobs == 0) return;
+  const uint32_t tid = threadIdx.x;
+  const uint32_t wg = tid >> 7, lt = tid & 127u;
+  const uint32_t lane_base = ((lt >> 5) * 32u) << 16;
+  const float scale = load_scale<T>(p.scale, p.scale_is_tensor, g.h);
+  const bool any_table = p.has_bias || p.has_mask;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  float* rk_arr = reinterpret_cast<float*>(smem_ptr + p.off_rk);
+  float* rowstats = reinterpret_cast<float*>(smem_ptr + p.off_rowstats);
+  const uint32_t NKV = p.n_kv_stages, NDS = p.n_ds_bufs, NBM = p.n_bm_stages;
+  const uint32_t tm_st = tmem + lane_base + wg * 128u + kTmST;
+  const uint32_t tm_dpt = tmem + lane_base + wg * 128u + kTmDPT;
+
+  // ---- K of a job: normalise in place, remember 1 / |k| ----
+  auto prologue_job = [&](uint32_t jtn) -> bool {
+    const uint32_t kvs = jtn % NKV;
+    const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
+    if (!mbar_wait(bar(kbKvFull + kvs), (jtn / NKV) & 1u, ctx, 50)) return false;
+    for (uint32_t rr = tid; rr < static_cast<uint32_t>(p.rows_kv); rr += 256u)
+      rk_arr[kvs * p.rows_kv + rr] = normalise_row<T>(k_base, rr);
+    fence_proxy_async_smem();
+    mbar_arrive(bar(kbKvReady + kvs));
+    return true;
+  };
+  // ---- Q / dO of a query tile: warpgroup 0 normalises Q, warpgroup 1 computes delta and lse ----
+  auto prologue_tile = [&](const TileIt& it, uint32_t tqn) -> bool {
+    const uint32_t qs = tqn % kNumQdoStages;
+    const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
+    if (!mbar_wait(bar(kbQdoFull + qs), (tqn / kNumQdoStages) & 1u, ctx, 51)) return false;
+    if (wg == 0) {
+      normalise_row<T>(q_base, lt);
+      fence_proxy_async_smem();
+    } else {
+      const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
+      const int bw = bwd_bw(p, g, it.t, m);
+      const int ig = g.pair ? static_cast<int>(lt & 63u) : it.i * kTileRows + static_cast<int>(lt);
+      float l2 = INFINITY, dl = 0.f;
+      if (bw < p.BW && ig < g.N) {
+        const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t wd[4];
+          lds128(q_base + 2u * kBoxBytes + sw64_offset(lt, ch), wd);
+          const uint4 ov = ldg_nc_v4(orow + ch * 8);
+          const uint32_t wo[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            dl = fmaf(Elem<T>::lo(wd[i]), Elem<T>::lo(wo[i]), dl);
+            dl = fmaf(Elem<T>::hi(wd[i]), Elem<T>::hi(wo[i]), dl);
+          }
+        }
+        const float lse = p.lse[bw * p.lse_sbw + g.h * p.lse_sh + ig];
+        l2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
+      }
+      rowstats[qs * 256u + lt] = l2;
+      rowstats[qs * 256u + 128u + lt] = dl;
+    }
+    mbar_arrive(bar(kbQdoReady + qs));
+    return true;
+  };
+
+  uint32_t jt = 0, tq = 0, nst = 0, cbm = 0, kdkv = 0, kdq = 0;
+  TileIt cur{0, 0, 0};
+  if (!prologue_job(0)) return;
+  if (!prologue_tile(cur, 0)) return;
+
+  while (true) {
+    TileIt nxt = cur;
+    const bool has_next = tile_next(g, nxt);
+    // With two K/V stages the next job's K is normalised one tile ahead of its first use; with a
+    // single stage its load can only start once this job is finished, so it is done at the end.
+    bool defer_job = false;
+    if (has_next) {
+      if (nxt.t != cur.t) {
+        if (NKV >= 2) {
+          if (!prologue_job(jt + 1)) return;
+        } else {
+          defer_job = true;
+        }
+      }
+      if (!prologue_tile(nxt, tq + 1)) return;
+    }
+
+    // ------------------------------ my step of the current tile ------------------------------
+    const int nr = step_rows(g, cur.i, static_cast<int>(wg));
+    const uint32_t kvs = jt % NKV;
+    if (nr > 0) {
+      bool key_ok;
+      int jg;
+      if (g.pair) {
+        const int m = static_cast<int>(lt >> 6);
+        key_ok = (m == static_cast<int>(wg)) && bwd_bw(p, g, cur.t, m) < p.BW &&
+                 static_cast<int>(lt & 63u) < g.N;
+        jg = static_cast<int>(lt & 63u);
+      } else {
+        jg = cur.j * kTileRows + static_cast<int>(lt);
+        key_ok = jg < g.N;
+      }
+      if (!mbar_wait(bar(kbStFull + wg), nst & 1u, ctx, 52)) return;
+      const uint32_t dsb = tq % NDS;
+      if (!mbar_wait(bar(kbDsFree + dsb), ((tq / NDS) & 1u) ^ 1u, ctx, 53)) return;
+      tc_fence_after();
+      const uint32_t ds_slab = smem_base + p.off_ds + dsb * kDsTileBytes + wg * 16384u;
+      const uint32_t qs = tq % kNumQdoStages;
+      const float* lse2 = rowstats + qs * 256u + wg * 64u;
+      const float* delta = rowstats + qs * 256u + 128u + wg * 64u;
+      const long long db_buf = g.pair ? 2ll * blockIdx.x + wg : static_cast<long long>(blockIdx.x);
+      const int ig0 = g.pair ? 0 : cur.i * kTileRows + static_cast<int>(wg) * kStepCols;
+      float* db_row = (p.has_bias && key_ok)
+                          ? p.db_partial + db_buf * p.db_buf_stride + static_cast<long long>(jg) * p.db_pitch + ig0
+                          : nullptr;
+      const bool db_store = (jt == 0);
+
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pw[16], dw[16];
+        const int rows_left = nr - kChunkCols * c;
+        if (rows_left > 0) {
+          uint32_t sv[32], dpv[32];
+          tmem_ld32(tm_st + 32u * c, sv);
+          tmem_ld32(tm_dpt + 32u * c, dpv);
+          tmem_wait_ld();
+          uint32_t bias_tile = 0, mask_tile = 0;
+          const uint32_t st = cbm % NBM;
+          if (any_table) {
+            bias_tile = smem_base + p.off_bm + (wg * NBM + st) * (2u * kTableTileBytes);
+            mask_tile = bias_tile + kTableTileBytes;
+            if (!mbar_wait(bar(kbBmFull + 2 * wg + st), (cbm / NBM) & 1u, ctx, 54)) return;
+          }
+          float* dbp = db_row != nullptr ? db_row + kChunkCols * c : nullptr;
+          if (rows_left >= kChunkCols)
+            bwd_chunk<T, false>(p.has_bias, p.has_mask, sv, dpv, bias_tile, mask_tile, lt,
+                                lse2 + 32 * c, delta + 32 * c, scale, rows_left, dbp, db_store, pw, dw);
+          else
+            bwd_chunk<T, true>(p.has_bias, p.has_mask, sv, dpv, bias_tile, mask_tile, lt,
+                               lse2 + 32 * c, delta + 32 * c, scale, rows_left, dbp, db_store, pw, dw);
+          if (any_table) {
+            mbar_arrive(bar(kbBmFree + 2 * wg + st));
+            ++cbm;
+          }
+          if (!key_ok) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { pw[i] = 0u; dw[i] = 0u; }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { pw[i] = 0u; dw[i] = 0u; }
+        }
+        tmem_st16(tm_st + 16u * c, pw);
+        tmem_st16(tm_dpt + 16u * c, dw);
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+          const uint32_t w4[4] = {dw[qd * 4], dw[qd * 4 + 1], dw[qd * 4 + 2], dw[qd * 4 + 3]};
+          sts128(ds_slab + sw128_offset(lt, 4u * c + qd), w4);
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(bar(kbPtFull + wg));
+      ++nst;
+    }
+
+    // ------------------------------ epilogues ------------------------------
+    if (cur.i == g.MT - 1) {
+      // dK, dV of key block cur.j are complete
+      if (!mbar_wait(bar(kbDkvFull), kdkv & 1u, ctx, 55)) return;
+      ++kdkv;
+      tc_fence_after();
+      const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
+      const int bw = bwd_bw(p, g, cur.t, m);
+      const int jg = g.pair ? static_cast<int>(lt & 63u) : cur.j * kTileRows + static_cast<int>(lt);
+      const bool ok = bw < p.BW && jg < g.N;
+      uint32_t r[32];
+      tmem_ld32(tmem + lane_base + (wg == 0 ? kTmDV : kTmDK), r);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar(kbDkvFree));
+      if (wg == 0) {
+        if (ok) {
+          uint16_t* dst = static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + jg * p.dv_sn;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 v;
+            v.x = Elem<T>::pack(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
+            v.y = Elem<T>::pack(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
+            v.z = Elem<T>::pack(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
+            v.w = Elem<T>::pack(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + ch * 8) = v;
+          }
+        }
+      } else {
+        // dk = scale * (dK' - k^ (k^ . dK')) / |k|
+        const uint32_t krow = g.pair ? lt : static_cast<uint32_t>(cur.j) * kTileRows + lt;
+        const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
+        float kh[32];
+        float dot = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t w[4];
+          lds128(k_base + sw64_offset(krow, ch), w);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            kh[ch * 8 + 2 * i] = Elem<T>::lo(w[i]);
+            kh[ch * 8 + 2 * i + 1] = Elem<T>::hi(w[i]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dot = fmaf(kh[i], __uint_as_float(r[i]), dot);
+        const float f = scale * rk_arr[kvs * p.rows_kv + krow];
+        if (ok) {
+          uint16_t* dst = static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + jg * p.dk_sn;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            float o8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              o8[i] = f * (__uint_as_float(r[ch * 8 + i]) - kh[ch * 8 + i] * dot);
+            uint4 v;
+            v.x = Elem<T>::pack(o8[0], o8[1]);
+            v.y = Elem<T>::pack(o8[2], o8[3]);
+            v.z = Elem<T>::pack(o8[4], o8[5]);
+            v.w = Elem<T>::pack(o8[6], o8[7]);
+            *reinterpret_cast<uint4*>(dst + ch * 8) = v;
+          }
+        }
+      }
+      if (cur.j == g.KB - 1) mbar_arrive(bar(kbKvFree + kvs));   // K^ in shared memory no longer needed
+
+      if (cur.j == g.KB - 1) {
+        // dQ of every query tile of the job is complete
+        if (!mbar_wait(bar(kbDqFull), kdq & 1u, ctx, 56)) return;
+        ++kdq;
+        tc_fence_after();
+        for (int i = static_cast<int>(wg); i < g.MT; i += 2) {
+          const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
+          const int bwq = bwd_bw(p, g, cur.t, mq);
+          const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
+          const bool okq = bwq < p.BW && ig < g.N;
+          uint32_t rq[32];
+          tmem_ld32(tmem + lane_base + kTmDQ + 32u * i, rq);
+          tmem_wait_ld();
+          if (okq) {
+            const uint16_t* qrow = static_cast<const uint16_t*>(p.q) + bwq * p.q_sbw + g.h * p.q_sh + ig * p.q_sn;
+            float qv[32];
+            float ss = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              const uint4 v = ldg_nc_v4(qrow + ch * 8);
+              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                qv[ch * 8 + 2 * e] = Elem<T>::lo(w[e]);
+                qv[ch * 8 + 2 * e + 1] = Elem<T>::hi(w[e]);
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ss = fmaf(qv[e], qv[e], ss);
+            const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+            float dot = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              qv[e] *= rn;
+              dot = fmaf(qv[e], __uint_as_float(rq[e]), dot);
+            }
+            dscale_acc += dot;
+            const float f = scale * rn;
+            uint16_t* dst = static_cast<uint16_t*>(p.dq) + bwq * p.dq_sbw + g.h * p.dq_sh + ig * p.dq_sn;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              float o8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                o8[e] = f * (__uint_as_float(rq[ch * 8 + e]) - qv[ch * 8 + e] * dot);
+              uint4 v;
+              v.x = Elem<T>::pack(o8[0], o8[1]);
+              v.y = Elem<T>::pack(o8[2], o8[3]);
+              v.z = Elem<T>::pack(o8[4], o8[5]);
+              v.w = Elem<T>::pack(o8[6], o8[7]);
+              *reinterpret_cast<uint4*>(dst + ch * 8) = v;
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar(kbDqFree));
+      }
+    }
+
+    if (!has_next) break;
+    if (defer_job) {
+      if (!prologue_job(jt + 1)) return;
+    }
+    if (nxt.t != cur.t) ++jt;
+    ++tq;
+    cur = nxt;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// MMA issuer (one thread)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
+                             const WaitCtx& ctx) {
+  const BwdGeom g = bwd_geom(p);
+  if (g.njobs == 0) return;
+  constexpr uint32_t fmt = Elem<T>::kFmt;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const uint32_t NKV = p.n_kv_stages, NDS = p.n_ds_bufs;
+  const uint32_t idesc_acc = make_idesc(fmt, 128, 32, 0, 1);   // A in TMEM, B MN-major
+  const uint32_t idesc_dq = make_idesc(fmt, 128, 32, 1, 1);    // A and B MN-major
+
+  auto stage_bases = [&](uint32_t jtn, uint32_t tqn, uint32_t& k_base, uint32_t& v_base,
+                         uint32_t& q_base, uint32_t& do_base) {
+    k_base = smem_base + p.off_kv + (jtn % NKV) * p.kv_stage_bytes;
+    v_base = k_base + static_cast<uint32_t>(p.rows_kv) * kRowBytes;
+    q_base = smem_base + p.off_qdo + (tqn % kNumQdoStages) * kQdoStageBytes;
+    do_base = q_base + 2u * kBoxBytes;
+  };
+  // S^T = K^ Q^^T and dP^T = V dO^T for step w of a tile
+  auto issue_sdp = [&](const TileIt& it, int w, uint32_t jtn, uint32_t tqn) {
+    const int nr = step_rows(g, it.i, w);
+    const uint32_t n16 = static_cast<uint32_t>(min(kStepCols, ((nr + 15) / 16) * 16));
+    uint32_t k_base, v_base, q_base, do_base;
+    stage_bases(jtn, tqn, k_base, v_base, q_base, do_base);
+    const uint32_t key_off = g.pair ? 0u : static_cast<uint32_t>(it.j) * kTileRows * kRowBytes;
+    const uint32_t row_off = static_cast<uint32_t>(w) * kStepCols * kRowBytes;
+    const uint32_t idesc = make_idesc(fmt, 128, n16, 0, 0);
+#pragma unroll
+    for (uint32_t k = 0; k < 2; ++k)
+      mma_ss(tmem + w * 128u + kTmST, make_smem_desc(k_base + key_off + k * 32u, 16, 512, kSw64),
+             make_smem_desc(q_base + row_off + k * 32u, 16, 512, kSw64), idesc, k);
+#pragma unroll
+    for (uint32_t k = 0; k < 2; ++k)
+      mma_ss(tmem + w * 128u + kTmDPT, make_smem_desc(v_base + key_off + k * 32u, 16, 512, kSw64),
+             make_smem_desc(do_base + row_off + k * 32u, 16, 512, kSw64), idesc, k);
+    mma_commit(bar(kbStFull + w));
+  };
+
+  uint32_t jt = 0, tq = 0, kdkv = 0, kdq = 0;
+  uint32_t nst[2] = {0u, 0u};
+  TileIt cur{0, 0, 0};
+  if (!mbar_wait(bar(kbKvReady + 0), 0u, ctx, 60)) return;
+  if (!mbar_wait(bar(kbQdoReady + 0), 0u, ctx, 61)) return;
+  tc_fence_after();
+  for (int w = 0; w < 2; ++w)
+    if (step_rows(g, cur.i, w) > 0) issue_sdp(cur, w, 0, 0);
+
+  while (true) {
+    TileIt nxt = cur;
+    const bool has_next = tile_next(g, nxt);
+    const bool cross = has_next && nxt.t != cur.t;
+    const uint32_t jt_next = cross ? jt + 1 : jt;
+    // Scores of the next tile are issued right behind this tile's dV / dK products, except across
+    // a job boundary when K of the next job cannot be ready yet (single K/V stage).
+    const bool look_now = has_next && !(cross && NKV < 2);
+    uint32_t k_base, v_base, q_base, do_base;
+    stage_bases(jt, tq, k_base, v_base, q_base, do_base);
+
+    if (cur.i == 0) {
+      // the previous key block's dK / dV must have been read out before they are overwritten
+      if (!mbar_wait(bar(kbDkvFree), (kdkv & 1u) ^ 1u, ctx, 62)) return;
+      if (cur.j == 0) {
+        if (!mbar_wait(bar(kbDqFree), (kdq & 1u) ^ 1u, ctx, 63)) return;
+      }
+    }
+    for (int w = 0; w < 2; ++w) {
+      if (step_rows(g, cur.i, w) > 0) {
+        if (!mbar_wait(bar(kbPtFull + w), nst[w] & 1u, ctx, 64)) return;
+        ++nst[w];
+        tc_fence_after();
+        const uint32_t row_off = static_cast<uint32_t>(w) * kStepCols * kRowBytes;
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k) {
+          const uint32_t acc = (cur.i > 0 || w > 0 || k > 0) ? 1u : 0u;
+          mma_ts(tmem + kTmDV, tmem + w * 128u + kTmST + k * 8u,
+                 make_smem_desc(do_base + row_off + k * 1024u, 512, 512, kSw64), idesc_acc, acc);
+        }
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k) {
+          const uint32_t acc = (cur.i > 0 || w > 0 || k > 0) ? 1u : 0u;
+          mma_ts(tmem + kTmDK, tmem + w * 128u + kTmDPT + k * 8u,
+                 make_smem_desc(q_base + row_off + k * 1024u, 512, 512, kSw64), idesc_acc, acc);
+        }
+      }
+      if (look_now) {
+        if (w == 0) {
+          if (cross) {
+            if (!mbar_wait(bar(kbKvReady + jt_next % NKV), (jt_next / NKV) & 1u, ctx, 65)) return;
+          }
+          const uint32_t tqn = tq + 1;
+          if (!mbar_wait(bar(kbQdoReady + tqn % kNumQdoStages), (tqn / kNumQdoStages) & 1u, ctx, 66)) return;
+          tc_fence_after();
+        }
+        if (step_rows(g, nxt.i, w) > 0) issue_sdp(nxt, w, jt_next, tq + 1);
+      }
+    }
+    // dQ^ of query tile cur.i += dS K^ (key block cur.j)
+    {
+      const uint32_t ds_base = smem_base + p.off_ds + (tq % NDS) * kDsTileBytes;
+      const uint32_t key_off = g.pair ? 0u : static_cast<uint32_t>(cur.j) * kTileRows * kRowBytes;
+#pragma unroll
+      for (uint32_t k = 0; k < 8; ++k) {
+        const uint32_t acc = (cur.j > 0 || k > 0) ? 1u : 0u;
+        mma_ss(tmem + kTmDQ + 32u * cur.i, make_smem_desc(ds_base + k * 2048u, 16384, 1024, kSw128),
+               make_smem_desc(k_base + key_off + k * 1024u, 512, 512, kSw64), idesc_dq, acc);
+      }
+    }
+    mma_commit(bar(kbDsFree + tq % NDS));
+    mma_commit(bar(kbQdoFree + tq % kNumQdoStages));
+    if (cur.i == g.MT - 1) {
+      mma_commit(bar(kbDkvFull));
+      ++kdkv;
+      if (cur.j == g.KB - 1) {
+        mma_commit(bar(kbDqFull));
+        ++kdq;
+        mma_commit(bar(kbKvFree + jt % NKV));
+      }
+    }
+    if (!has_next) break;
+    if (!look_now) {
+      if (!mbar_wait(bar(kbKvReady + jt_next % NKV), (jt_next / NKV) & 1u, ctx, 67)) return;
+      const uint32_t tqn = tq + 1;
+      if (!mbar_wait(bar(kbQdoReady + tqn % kNumQdoStages), (tqn / kNumQdoStages) & 1u, ctx, 68)) return;
+      tc_fence_after();
+      for (int w = 0; w < 2; ++w)
+        if (step_rows(g, nxt.i, w) > 0) issue_sdp(nxt, w, jt_next, tq + 1);
+    }
+    jt = jt_next;
+    ++tq;
+    cur = nxt;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// TMA producer (one thread): three independent streams, none of which ever blocks the others.
+//   (a)  K/V of a job, then Q/dO of each of its tiles
+//   (b0) bias^T / mask^T chunks for warpgroup 0     (b1) the same for warpgroup 1
+// ------------------------------------------------------------------------------------------------
+struct BmCursor {
+  TileIt it;
+  int c;
+  uint32_t cc;
+  bool done;
+};
+
+__device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t bars,
+                              const WaitCtx& ctx) {
+  const BwdGeom g = bwd_geom(p);
+  if (g.njobs == 0) return;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const uint32_t NKV = p.n_kv_stages, NBM = p.n_bm_stages;
+  const bool any_table = p.has_bias || p.has_mask;
+  const uint32_t ntab = (p.has_bias ? 1u : 0u) + (p.has_mask ? 1u : 0u);
+
+  // stream (a)
+  TileIt a_it{0, 0, 0};
+  bool a_kv_pending = true, a_done = false;
+  uint32_t a_jt = 0, a_tq = 0;
+  // streams (b0), (b1)
+  BmCursor bc[2];
+  auto bm_seek = [&](BmCursor& b, int w) {
+    // move to the next existing (step, chunk) at or after the current position
+    while (!b.done) {
+      const int nr = step_rows(g, b.it.i, w);
+      if (nr > 0 && nr - kChunkCols * b.c > 0 && b.c < 2) return;
+      b.c = 0;
+      if (!tile_next(g, b.it)) b.done = true;
+      else if (step_rows(g, b.it.i, w) > 0) return;
+    }
+  };
+  for (int w = 0; w < 2; ++w) {
+    bc[w].it = TileIt{0, 0, 0};
+    bc[w].c = 0;
+    bc[w].cc = 0;
+    bc[w].done = !any_table;
+    if (!bc[w].done) bm_seek(bc[w], w);
+  }
+
+  long long t0 = clock64();
+  uint32_t idle = 0;
+  while (!a_done || !bc[0].done || !bc[1].done) {
+    bool progress = false;
+    if (!a_done) {
+      if (a_kv_pending) {
+        const uint32_t kvs = a_jt % NKV;
+        if (mbar_try_wait(bar(kbKvFree + kvs), ((a_jt / NKV) & 1u) ^ 1u)) {
+          const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
+          const uint32_t v_base = k_base + static_cast<uint32_t>(p.rows_kv) * kRowBytes;
+          const uint32_t full = bar(kbKvFull + kvs);
+          mbar_arrive_expect_tx(full, 2u * static_cast<uint32_t>(p.rows_kv) * kRowBytes);
+          const int nbox = p.rows_kv / kBoxRows;
+          for (int b = 0; b < nbox; ++b) {
+            const int bw = g.pair ? bwd_bw(p, g, a_it.t, b) : bwd_bw(p, g, a_it.t, 0);
+            const int r0 = g.pair ? 0 : b * kBoxRows;
+            tma_load_4d(k_base + b * kBoxBytes, &p.tm_k, full, 0, r0, g.h, bw);
+            tma_load_4d(v_base + b * kBoxBytes, &p.tm_v, full, 0, r0, g.h, bw);
+          }
+          a_kv_pending = false;
+          progress = true;
+        }
+      } else {
+        const uint32_t qs = a_tq % kNumQdoStages;
+        if (mbar_try_wait(bar(kbQdoFree + qs), ((a_tq / kNumQdoStages) & 1u) ^ 1u)) {
+          const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
+          const uint32_t full = bar(kbQdoFull + qs);
+          mbar_arrive_expect_tx(full, kQdoStageBytes);
+          for (int b = 0; b < 2; ++b) {
+            const int bw = g.pair ? bwd_bw(p, g, a_it.t, b) : bwd_bw(p, g, a_it.t, 0);
+            const int r0 = g.pair ? 0 : a_it.i * kTileRows + b * kBoxRows;
+            tma_load_4d(q_base + b * kBoxBytes, &p.tm_q, full, 0, r0, g.h, bw);
+            tma_load_4d(q_base + 2u * kBoxBytes + b * kBoxBytes, &p.tm_do, full, 0, r0, g.h, bw);
+          }
+          ++a_tq;
+          const int t_before = a_it.t;
+          if (!tile_next(g, a_it)) {
+            a_done = true;
+          } else if (a_it.t != t_before) {
+            ++a_jt;
+            a_kv_pending = true;
+          }
+          progress = true;
+        }
+      }
+    }
+    for (int w = 0; w < 2; ++w) {
+      BmCursor& b = bc[w];
+      if (b.done) continue;
+      const uint32_t st = b.cc % NBM;
+      if (!mbar_try_wait(bar(kbBmFree + 2 * w + st), ((b.cc / NBM) & 1u) ^ 1u)) continue;
+      const uint32_t base = smem_base + p.off_bm + (w * NBM + st) * (2u * kTableTileBytes);
+      const uint32_t full = bar(kbBmFull + 2 * w + st);
+      if (g.pair) {
+        // only the keys of unit w are looked at by warpgroup w
+        mbar_arrive_expect_tx(full, ntab * kBoxBytes);
+        const int bw = bwd_bw(p, g, b.it.t, w);
+        const int c0 = b.c * kChunkCols;
+        if (p.has_bias) tma_load_3d(base + w * kBoxBytes, &p.tm_biasT, full, c0, 0, g.h);
+        if (p.has_mask)
+          tma_load_3d(base + kTableTileBytes + w * kBoxBytes, &p.tm_maskT, full, c0, 0,
+                      bw < p.BW ? bw % p.nW : 0);
+      } else {
+        mbar_arrive_expect_tx(full, ntab * 2u * kBoxBytes);
+        const int bw = bwd_bw(p, g, b.it.t, 0);
+        const int c0 = b.it.i * kTileRows + w * kStepCols + b.c * kChunkCols;
+        for (int hb = 0; hb < 2; ++hb) {
+          const int r0 = b.it.j * kTileRows + hb * kBoxRows;
+          if (p.has_bias) tma_load_3d(base + hb * kBoxBytes, &p.tm_biasT, full, c0, r0, g.h);
+          if (p.has_mask)
+            tma_load_3d(base + kTableTileBytes + hb * kBoxBytes, &p.tm_maskT, full, c0, r0, bw % p.nW);
+        }
+      }
+      ++b.cc;
+      ++b.c;
+      bm_seek(b, w);
+      progress = true;
+    }
+    if (progress) {
+      idle = 0;
+    } else if ((++idle & 0x3Fu) == 0) {
+      if (idle == 0x40u) t0 = clock64();
+      if (*ctx.abort_flag) return;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *ctx.abort_flag = 1u;
+        if (ctx.status != nullptr) {
+          if (atomicCAS(&ctx.status->code, 0u, (70u << 8) | kStatusTimeout) == 0u) {
+            ctx.status->block = blockIdx.x;
+            ctx.status->detail = (a_tq << 16) | (bc[0].cc & 0xFFFFu);
+          }
+        }
+        return;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_constant__ BwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t tid = threadIdx.x;
+  const uint32_t warp = tid >> 5;
+  const uint32_t lane = tid & 31u;
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const uint32_t bars = smem_base + p.off_ctrl;
+  uint32_t* ctrl_words = reinterpret_cast<uint32_t*>(smem_raw + p.off_ctrl + 8u * kBwdNumBars);
+  uint32_t& tmem_slot = ctrl_words[0];
+  float* warp_sums = reinterpret_cast<float*>(&ctrl_words[4]);
+  if ((smem_base & 1023u) != 0u) {
+    if (tid == 0 && p.status != nullptr) atomicCAS(&p.status->code, 0u, (99u << 8) | 2u);
+    return;
+  }
+
+  if (tid == 0) {
+    ctrl_words[1] = 0u;
+    for (int i = 0; i < kBwdNumBars; ++i) {
+      uint32_t count = 1u;
+      if (i >= kbKvReady && i < kbKvFree) count = 256u;
+      else if (i >= kbKvFree && i < kbQdoFull) count = 257u;
+      else if (i >= kbQdoReady && i < kbQdoFree) count = 256u;
+      else if (i >= kbPtFull && i < kbBmFull) count = 128u;
+      else if (i >= kbBmFree && i < kbDsFree) count = 128u;
+      else if (i == kbDkvFree || i == kbDqFree) count = 256u;
+      mbar_init(bars + 8u * i, count);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&p.tm_q);
+    tma_prefetch_desc(&p.tm_k);
+    tma_prefetch_desc(&p.tm_v);
+    tma_prefetch_desc(&p.tm_do);
+    if (p.has_bias) tma_prefetch_desc(&p.tm_biasT);
+    if (p.has_mask) tma_prefetch_desc(&p.tm_maskT);
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(&tmem_slot), kBwdTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  WaitCtx ctx{&ctrl_words[1], p.status};
+
+  float dscale_acc = 0.f;
+  if (warp < 8) {
+    bwd_compute_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, dscale_acc);
+  } else if (lane == 0) {
+    if (warp == 8) bwd_mma_role<T>(p, smem_base, bars, tmem, ctx);
+    else bwd_load_role(p, smem_base, bars, ctx);
+  }
+  __syncwarp();
+  // deterministic CTA-wide sum of the dLogitScale contributions
+  if (warp < 8) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dscale_acc += __shfl_xor_sync(0xFFFFFFFFu, dscale_acc, off);
+    if (lane == 0) warp_sums[warp] = dscale_acc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && p.dscale_partial != nullptr) {
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += warp_sums[w];
+    p.dscale_partial[blockIdx.x] =
+        s * load_scale<T>(p.scale, p.scale_is_tensor, static_cast<int>(blockIdx.x) % p.H);
+  }
+  if (ctrl_words[1]) {
+    __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 8) tmem_dealloc(tmem, kBwdTmemCols);
+}
+
+template __global__ void bwd_kernel<__nv_bfloat16>(const __grid_constant__ BwdParams);
+template __global__ void bwd_kernel<__half>(const __grid_constant__ BwdParams);
+
+cudaError_t launch_bwd(const BwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream) {
+  auto go = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(p.smem_bytes));
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kBwdThreads, p.smem_bytes, stream>>>(p);
+    return cudaGetLastError();
+  };
+  return dtype_is_bf16 ? go(bwd_kernel<__nv_bfloat16>) : go(bwd_kernel<__half>);
+}
+
+}  // namespace fwa2

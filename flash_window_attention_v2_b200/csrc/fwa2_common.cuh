@@ -49,4 +49,88 @@ struct FwdParams {
   DeviceStatus* status;
 };
 
+// Normalise one 32-element row of a 64-byte-swizzled tile in place; returns 1 / max(|x|, 1e-12).
+template <typename T>
+__device__ __forceinline__ float normalise_row(uint32_t tile_base, uint32_t row) {
+  uint32_t w[4][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    lds128(tile_base + sw64_offset(row, ch), w[ch]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = Elem<T>::lo(w[ch][i]), b = Elem<T>::hi(w[ch][i]);
+      ss = fmaf(a, a, ss);
+      ss = fmaf(b, b, ss);
+    }
+  }
+  const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      w[ch][i] = Elem<T>::pack(Elem<T>::lo(w[ch][i]) * rn, Elem<T>::hi(w[ch][i]) * rn);
+    sts128(tile_base + sw64_offset(row, ch), w[ch]);
+  }
+  return rn;
+}
+
+// Multiplier of the cosine scores: exp(min(g_h, ln 100)) in tensor mode, the given fp32 constant
+// in scalar mode.
+template <typename T>
+__device__ __forceinline__ float load_scale(const void* scale, int is_tensor, int h) {
+  if (!is_tensor) return *static_cast<const float*>(scale);
+  const float g = Elem<T>::from_raw(static_cast<const uint16_t*>(scale)[h]);
+  return __expf(fminf(g, kLn100));
+}
+
+// Backward.  CTA c works on head (c mod H) only, on the windows slot, slot + nslots, ... with
+// slot = c / H, so that its window-summed dBias partial has a single writer per address.
+struct BwdParams {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do;   // 4-D (d, N, H, BW), box (32, 64, 1, 1)
+  CUtensorMap tm_biasT, tm_maskT;        // 3-D transposed tables (N_pad, N, planes), box (32, 64, 1)
+  const void* q;  long long q_sbw, q_sh, q_sn;
+  const void* k;  long long k_sbw, k_sh, k_sn;
+  const void* o;  long long o_sbw, o_sh, o_sn;
+  void* dq;       long long dq_sbw, dq_sh, dq_sn;
+  void* dk;       long long dk_sbw, dk_sh, dk_sn;
+  void* dv;       long long dv_sbw, dv_sh, dv_sn;
+  const float* lse;
+  long long lse_sbw, lse_sh;
+  const void* scale;
+  int scale_is_tensor;
+  float* db_partial;          // [n_bufs][N][db_pitch] fp32, transposed: (key, query)
+  long long db_buf_stride;    // N * db_pitch
+  int db_pitch;               // N rounded up to 32
+  float* dscale_partial;      // [grid]
+  int BW, H, N, nW;
+  int has_bias, has_mask;
+  int pair_mode;
+  int nslots;                 // grid = nslots * H
+  int n_kv_stages, n_ds_bufs, n_bm_stages;
+  int rows_kv;                // K/V rows held per stage (N rounded up to 128; 128 in pair mode)
+  uint32_t off_kv, kv_stage_bytes;   // stage = [K rows | V rows]
+  uint32_t off_qdo;                  // 2 stages of [Q tile 8 KiB | dO tile 8 KiB]
+  uint32_t off_ds;                   // n_ds_bufs tiles of 32 KiB (two 64-query slabs)
+  uint32_t off_bm;                   // [warpgroup][stage] of [bias^T 8 KiB | mask^T 8 KiB]
+  uint32_t off_rk;                   // n_kv_stages x rows_kv floats: 1 / |k|
+  uint32_t off_rowstats;             // 2 stages x (128 lse*log2e, 128 delta) floats
+  uint32_t off_ctrl;
+  uint32_t smem_bytes;
+  DeviceStatus* status;
+};
+
+// Second stage of the dBias / dLogitScale reduction.
+struct ReduceParams {
+  const float* db_partial;     // [n_bufs][N][pitch] (key, query)
+  long long buf_stride;
+  int pitch;
+  const float* dscale_partial; // [grid]
+  int H, N, BW, nslots, pair;
+  float* out_f32;              // (H*N*N + H) or nullptr
+  void* dbias;                 // (H, N, N) output dtype or nullptr
+  void* dscale;                // H values or nullptr
+  const void* logit_scale;     // for the gate (tensor mode) or nullptr
+};
+
 }  // namespace fwa2

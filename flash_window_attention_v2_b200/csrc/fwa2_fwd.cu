@@ -42,39 +42,6 @@ __device__ __forceinline__ FwdShape fwd_shape(const FwdParams& p) {
   return s;
 }
 
-// Normalise one 32-element row of a 64-byte-swizzled tile in place; returns 1 / max(|x|, 1e-12).
-template <typename T>
-__device__ __forceinline__ float normalise_row(uint32_t tile_base, uint32_t row) {
-  uint32_t w[4][4];
-  float ss = 0.f;
-#pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
-    lds128(tile_base + sw64_offset(row, ch), w[ch]);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float a = Elem<T>::lo(w[ch][i]), b = Elem<T>::hi(w[ch][i]);
-      ss = fmaf(a, a, ss);
-      ss = fmaf(b, b, ss);
-    }
-  }
-  const float rn = rsqrtf(fmaxf(ss, 1e-24f));
-#pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      w[ch][i] = Elem<T>::pack(Elem<T>::lo(w[ch][i]) * rn, Elem<T>::hi(w[ch][i]) * rn);
-    sts128(tile_base + sw64_offset(row, ch), w[ch]);
-  }
-  return rn;
-}
-
-template <typename T>
-__device__ __forceinline__ float load_scale(const FwdParams& p, int h) {
-  if (!p.scale_is_tensor) return *static_cast<const float*>(p.scale);
-  const float g = Elem<T>::from_raw(static_cast<const uint16_t*>(p.scale)[h]);
-  return __expf(fminf(g, kLn100));
-}
-
 // ------------------------------------------------------------------------------------------------
 // Softmax warps
 // ------------------------------------------------------------------------------------------------
@@ -111,7 +78,7 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
     const int unit = sh.pair ? 2 * job + static_cast<int>(hf) : job;
     const bool unit_ok = unit < sh.U;
     const int bw = unit / sh.H, h = unit - bw * sh.H;
-    const float scale = load_scale<T>(p, h);
+    const float scale = load_scale<T>(p.scale, p.scale_is_tensor, h);
 
     // ---- normalise the K rows of this job in place ----
     const uint32_t kvs = jt % p.n_kv_stages;

@@ -20,7 +20,7 @@ import torch
 
 from .. import _lib
 
-__all__ = ["_flash_attn_forward", "_flash_attn_backward", "check_device_status"]
+__all__ = ["_flash_attn_forward", "_flash_attn_backward", "check_device_status", "finalize_grads"]
 
 _DTYPES = {torch.float16: _lib.FWA2_F16, torch.bfloat16: _lib.FWA2_BF16}
 _status_words: dict[int, torch.Tensor] = {}
@@ -144,4 +144,104 @@ def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="
 def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, db,
                          bias=None, mask=None, scale_type="scalar", _partial_out=None,
                          _variant: int = 0, _max_ctas: int = 0):
-    raise NotImplementedError("backward kernel not built yet")
+    """Fills dq, dk, dv (and dscale, db when given) in place; returns None.
+
+    `_partial_out` (fp32, H*N*N + H elements) is an extension used by the window-sharded
+    multi-GPU path: when given, the window-summed dBias / dLogitScale are left there in fp32
+    (before the clamp gate and the cast) and `db` / `dscale` are not written.
+    """
+    if do.stride(-1) != 1:
+        do = do.contiguous()
+    batch_window_size, n_heads, seqlen_q, d = q.shape
+    _, _, seqlen_k, _ = k.shape
+    assert d <= 128
+    assert seqlen_q == seqlen_k
+    seqlen_q_rounded = math.ceil(seqlen_q / 64) * 64
+    assert lse.shape == (batch_window_size, n_heads, seqlen_q_rounded)
+    assert q.stride(-1) == k.stride(-1) == v.stride(-1) == o.stride(-1) == 1
+    assert dq.stride(-1) == dk.stride(-1) == dv.stride(-1) == 1
+    assert q.dtype in _DTYPES and q.dtype == k.dtype == v.dtype == o.dtype == do.dtype
+    has_bias = bias is not None
+    if has_bias:
+        assert bias.dtype in [q.dtype, torch.float]
+        assert bias.is_cuda
+        assert bias.shape == (n_heads, seqlen_q, seqlen_k)
+        assert db is not None or _partial_out is not None
+    n_windows = 0
+    if mask is not None:
+        assert mask.dtype in [q.dtype, torch.float]
+        assert mask.is_cuda
+        n_windows = mask.shape[0]
+    if scale_type == "tensor":
+        assert dscale is not None or _partial_out is not None
+        if not logit_scale.is_contiguous():
+            logit_scale = logit_scale.contiguous()
+
+    qc, kc, vc, oc, doc = _rows(q), _rows(k), _rows(v), _rows(o), _rows(do)
+    outs = []
+    for g in (dq, dk, dv):
+        outs.append(g if _tma_ok(g) else torch.empty(g.shape, device=g.device, dtype=g.dtype))
+    bias_t = _table(bias, q.dtype) if has_bias else None
+    mask_t = _table(mask, q.dtype) if mask is not None else None
+    db_c = db if (db is None or db.is_contiguous()) else torch.empty(db.shape, device=db.device, dtype=db.dtype)
+    ds_c = dscale if (dscale is None or dscale.is_contiguous()) else torch.empty(
+        dscale.shape, device=dscale.device, dtype=dscale.dtype)
+
+    L = _lib.lib()
+    with torch.cuda.device(q.device):
+        ws_bytes = L.fwa2_bwd_workspace_bytes(batch_window_size, n_heads, seqlen_q, n_windows,
+                                              1 if has_bias else 0, 1 if mask is not None else 0)
+        assert ws_bytes > 0
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+
+        a = _lib.BwdArgs()
+        a.struct_size = C.sizeof(_lib.BwdArgs)
+        a.abi_version = _lib.FWA2_ABI_VERSION
+        a.dtype = _DTYPES[q.dtype]
+        a.bw, a.heads, a.n, a.head_dim = batch_window_size, n_heads, seqlen_q, d
+        a.n_windows = n_windows
+        a.q, a.k, a.v, a.o, a.dout = _t4(qc), _t4(kc), _t4(vc), _t4(oc), _t4(doc)
+        a.dq, a.dk, a.dv = _t4(outs[0]), _t4(outs[1]), _t4(outs[2])
+        a.lse = lse.data_ptr()
+        a.lse_stride_bw, a.lse_stride_h = lse.stride(0), lse.stride(1)
+        a.logit_scale = logit_scale.data_ptr()
+        a.scale_is_tensor = 1 if scale_type == "tensor" else 0
+        a.bias = bias_t.data_ptr() if bias_t is not None else None
+        a.mask = mask_t.data_ptr() if mask_t is not None else None
+        a.bias_row_stride = bias_t.stride(1) if bias_t is not None else 0
+        a.mask_row_stride = mask_t.stride(1) if mask_t is not None else 0
+        a.dbias = db_c.data_ptr() if (db_c is not None and has_bias) else None
+        a.dscale = ds_c.data_ptr() if (ds_c is not None and scale_type == "tensor") else None
+        a.partial_out = _partial_out.data_ptr() if _partial_out is not None else None
+        a.workspace = workspace.data_ptr()
+        a.workspace_bytes = ws_bytes
+        a.status = _status(q.device).data_ptr()
+        a.variant = _variant
+        a.max_ctas = _max_ctas
+        _lib.check(L.fwa2_backward(C.byref(a), _stream(q.device)), "fwa2_backward")
+
+    for dst, src in zip((dq, dk, dv), outs):
+        if dst is not src:
+            dst.copy_(src)
+    if db is not None and db_c is not db:
+        db.copy_(db_c)
+    if dscale is not None and ds_c is not dscale:
+        dscale.copy_(ds_c)
+    return None
+
+
+def finalize_grads(partial, logit_scale, db, dscale):
+    """Cast an fp32 [H*N*N dBias | H dLogitScale] buffer (possibly summed over GPUs) into
+    `db` / `dscale`, applying 1[g <= ln 100] to dLogitScale."""
+    h = db.shape[0] if db is not None else dscale.shape[0]
+    n = db.shape[-1] if db is not None else int(round(math.sqrt((partial.numel() - h) / h)))
+    ref = db if db is not None else dscale
+    assert partial.dtype == torch.float32 and partial.is_contiguous()
+    assert db is None or db.is_contiguous()
+    with torch.cuda.device(partial.device):
+        _lib.check(_lib.lib().fwa2_finalize_grads(
+            partial.data_ptr(), _DTYPES[ref.dtype], h, n,
+            logit_scale.data_ptr() if dscale is not None else None,
+            db.data_ptr() if db is not None else None,
+            dscale.data_ptr() if dscale is not None else None,
+            _stream(partial.device)), "fwa2_finalize_grads")
