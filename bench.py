@@ -1,0 +1,351 @@
+#!/usr/bin/env python
+"""Benchmark of the window-attention hot path: forward + backward TFLOP/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config cfg2] [--impl ours|reference]
+
+One "step" is one forward + backward pass of the op over one batch of synthetic windows, through
+the public autograd API.  With N > 1 (launched by torch.distributed.run, one rank per GPU) every
+rank works on its own full-size batch (weak scaling); the only exchange step is the all-reduce of
+dBias / dLogitScale inside backward.  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the reference's classic PyTorch path on the host CPU cores (the
+multi-threaded port in oracle/classic_cpu.py) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from flash_window_attention_v2_b200.workloads import CONFIGS, make_inputs, sweep  # noqa: E402
+
+METRIC = "fwd+bwd window-attention throughput (matmul FLOPs 14*N^2*d per window-head)"
+UNIT = "TFLOP/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                parts = [x.strip() for x in out.stdout.strip().split(",")]
+                if len(parts) >= 7:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(s[0]) for s in self.samples)
+        reasons = []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for i, nme in enumerate(names):
+            if any(s[3 + i].lower().startswith("active") for s in self.samples):
+                reasons.append(nme)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.samples[0][1]),
+                "power_w_max": max(float(s[2]) for s in self.samples), "samples": len(sm), "reasons": reasons}
+
+
+def cpu_baseline(w, seconds: float = 12.0, sample_images: int | None = None):
+    """Times oracle/classic_cpu.py (fp32, all host threads) on `sample_images` images of `w`."""
+    from oracle import classic_cpu
+    if sample_images is None:
+        # aim at roughly a second per pass: the classic path materialises (BW, H, N, N) fp32
+        per_image = w.nw * w.heads * w.n * w.n * 4
+        sample_images = max(1, min(w.batch, int(1.5e8 // per_image)))
+    t = make_inputs(w, seed=0, batch=sample_images)
+    f = {k: (v.float() if v is not None else None) for k, v in t.items()}
+    flops = 14.0 * w.n * w.n * w.head_dim * sample_images * w.nw * w.heads
+    classic_cpu.forward_backward(f["q"], f["k"], f["v"], f["do"], f["logit_scale"], f["bias"], f["mask"])
+    n, t0 = 0, time.perf_counter()
+    while True:
+        classic_cpu.forward_backward(f["q"], f["k"], f["v"], f["do"], f["logit_scale"], f["bias"], f["mask"])
+        n += 1
+        el = time.perf_counter() - t0
+        if el >= seconds or n >= 200:
+            break
+    return dict(value=flops * n / el / 1e12, unit=UNIT, cores=torch.get_num_threads(), kind="port",
+                sample=f"{sample_images} of {w.batch} images ({sample_images * w.nw * w.heads} window-heads), "
+                       f"{n} passes in {el:.1f} s, fp32, host cpu_count={os.cpu_count()}",
+                seconds_per_full_step=el / n * w.batch / sample_images)
+
+
+def run_reference(args, w, rank):
+    """The reference arm: its classic path on the host cores; rank 0 only."""
+    if rank != 0:
+        return
+    per_image = w.nw * w.heads * w.n * w.n * 4
+    sample_images = max(1, min(w.batch, int(1.5e8 // per_image)))
+    from oracle import classic_cpu
+    t = make_inputs(w, seed=0, batch=sample_images)
+    f = {k: (v.float() if v is not None else None) for k, v in t.items()}
+    flops = 14.0 * w.n * w.n * w.head_dim * sample_images * w.nw * w.heads
+    for _ in range(max(1, min(args.warmup, 3))):
+        classic_cpu.forward_backward(f["q"], f["k"], f["v"], f["do"], f["logit_scale"], f["bias"], f["mask"])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        classic_cpu.forward_backward(f["q"], f["k"], f["v"], f["do"], f["logit_scale"], f["bias"], f["mask"])
+    el = time.perf_counter() - t0
+    val = flops * args.steps / el / 1e12
+    sample = (f"each step = {sample_images} of {w.batch} images ({sample_images * w.nw * w.heads} window-heads) "
+              f"of {w.name}, fp32 classic path on host cores")
+    line = dict(impl="reference", metric=METRIC, value=val, unit=UNIT, n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=el / args.steps * 1e3, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=w.name, window_heads_per_step=sample_images * w.nw * w.heads, n=w.n,
+                            head_dim=w.head_dim),
+                cpu_baseline=dict(value=val, unit=UNIT, cores=torch.get_num_threads(), kind="port", sample=sample),
+                e2e=dict(value=val, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="cfg2", help="cfg2 | cfg3 | cfg4 | sweep_w<window>")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the extra single-GPU configurations")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    w = CONFIGS[args.config] if args.config in CONFIGS else sweep(int(args.config.split("_w")[1]))
+
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    import torch.distributed as dist
+    from flash_window_attention_v2_b200 import flash_win_attn_v2_func
+    from flash_window_attention_v2_b200 import kernels as K
+    from flash_window_attention_v2_b200.sharded import sharded_flash_win_attn_v2_func
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def flush_l2():
+        flush_buf.zero_()
+
+    def make_step(wl, t):
+        q, k, v = (t[x].requires_grad_(True) for x in ("q", "k", "v"))
+        ls = t["logit_scale"].requires_grad_(True)
+        bias = t["bias"].requires_grad_(True)
+        wrt = (q, k, v, ls, bias)
+
+        def step():
+            if world > 1:
+                o = sharded_flash_win_attn_v2_func(q, k, v, ls, bias, t["mask"])
+            else:
+                o = flash_win_attn_v2_func(q, k, v, ls, bias, t["mask"])
+            return (o,) + torch.autograd.grad(o, wrt, t["do"])
+        return step
+
+    def time_steps(step, steps, warmup):
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        barrier()
+        evs = []
+        for _ in range(steps):
+            flush_l2()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            step()
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        barrier()
+        ms = sum(a.elapsed_time(b) for a, b in evs)
+        if world > 1:
+            tt = torch.tensor([ms], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        return ms / steps
+
+    def kernel_times(wl, t, steps, warmup):
+        """Device time of the forward kernel and of the backward main kernel alone (bare boundary
+        calls, L2 flushed before every launch)."""
+        q, k, v, do, ls = t["q"].detach(), t["k"].detach(), t["v"].detach(), t["do"], t["logit_scale"].detach()
+        bias, mask = t["bias"].detach(), t["mask"]
+        o, lse, _ = K._flash_attn_forward(q, k, v, ls, bias=bias, mask=mask, scale_type="tensor")
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        db, dscale = torch.empty_like(bias), torch.empty_like(ls)
+        ws_bytes = K._lib.lib().fwa2_bwd_workspace_bytes(q.shape[0], q.shape[1], q.shape[2], mask.shape[0], 1, 1)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        bwd_full = lambda variant: K._flash_attn_backward(do, q, k, v, ls, o, lse, dq, dk, dv, dscale, db, bias=bias,
+                                                          mask=mask, scale_type="tensor", _variant=variant,
+                                                          _workspace=ws)
+        bwd_full(0)
+        fwd = lambda: K._flash_attn_forward(q, k, v, ls, bias=bias, mask=mask, scale_type="tensor")
+        res = {}
+        for name, fn in (("fwd", fwd), ("bwd_main", lambda: bwd_full(2 | 4)), ("bwd_all", lambda: bwd_full(0))):
+            for _ in range(warmup):
+                fn()
+            torch.cuda.synchronize()
+            evs = []
+            for _ in range(steps):
+                flush_l2()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                evs.append((a, b))
+            torch.cuda.synchronize()
+            res[name] = sum(a.elapsed_time(b) for a, b in evs) / steps
+        K.check_device_status(dev)
+        return res
+
+    # ------------------------------------------------------------------ the headline workload
+    t = make_inputs(w, seed=rank, device=dev)
+    step = make_step(w, t)
+    with ClockSampler(local_rank) as clocks:
+        ms_step = time_steps(step, args.steps, max(args.warmup, 3))
+        kt = kernel_times(w, t, max(5, args.steps // 2), 3) if rank == 0 or world == 1 else None
+    K.check_device_status(dev)
+    flops_rank = w.matmul_flops()
+    value = flops_rank * world / (ms_step * 1e-3) / 1e12
+
+    # ------------------------------------------------------------------ end to end, host buffers
+    host = {kk: (vv.detach().cpu().pin_memory() if vv is not None else None) for kk, vv in t.items()}
+    dev_in = {kk: (torch.empty_like(t[kk]) if vv is not None else None) for kk, vv in t.items()}
+    outs_host = None
+
+    def e2e_step():
+        nonlocal outs_host
+        for kk, vv in host.items():
+            if vv is not None:
+                dev_in[kk].copy_(vv, non_blocking=True)
+        tt = {kk: (vv.detach() if vv is not None else None) for kk, vv in dev_in.items()}
+        res = make_step(w, tt)()
+        if outs_host is None:
+            outs_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+        for hbuf, r in zip(outs_host, res):
+            hbuf.copy_(r, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e = time_steps(e2e_step, e2e_steps, 2)
+    h2d = sum(v.numel() * v.element_size() for v in host.values() if v is not None)
+    d2h = sum(b.numel() * b.element_size() for b in outs_host)
+    e2e_val = flops_rank * world / (ms_e2e * 1e-3) / 1e12
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ------------------------------------------------------------------ roofline of the dominant kernel
+    bwd_bytes = w.algorithmic_bytes(fwd=False, bwd=True)
+    ach = bwd_bytes / (kt["bwd_main"] * 1e-3) / 1e9
+    roofline = dict(bound="hbm", kernel="bwd_kernel", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s",
+                    frac=ach / peaks["hbm_gbs"], peak_source=peaks["source"], traffic=None,
+                    launch_ms=kt["bwd_main"], algorithmic_bytes_per_launch=bwd_bytes,
+                    fwd_kernel=dict(launch_ms=kt["fwd"],
+                                    achieved=w.algorithmic_bytes(True, False) / (kt["fwd"] * 1e-3) / 1e9,
+                                    frac=w.algorithmic_bytes(True, False) / (kt["fwd"] * 1e-3) / 1e9 / peaks["hbm_gbs"]),
+                    bwd_call_ms=kt["bwd_all"],
+                    tensor_frac_of_bf16_peak=w.matmul_flops() / ((kt["fwd"] + kt["bwd_all"]) * 1e-3) / 1e12
+                    / peaks["bf16_tflops"])
+
+    extra = {}
+    if not args.no_extra and world == 1:
+        for name in ("cfg3", "cfg4", "cfg2"):
+            if name == w.name:
+                continue
+            wl = CONFIGS[name]
+            tx = make_inputs(wl, seed=0, device=dev)
+            ms = time_steps(make_step(wl, tx), 10, 3)
+            ktx = kernel_times(wl, tx, 5, 2)
+            extra[name] = dict(dtype=wl.dtype, n=wl.n, window_heads=wl.units, ms_per_step=ms,
+                               tflops=wl.matmul_flops() / (ms * 1e-3) / 1e12,
+                               frac_bf16_peak=wl.matmul_flops() / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                               fwd_kernel_ms=ktx["fwd"], bwd_kernel_ms=ktx["bwd_main"], bwd_call_ms=ktx["bwd_all"],
+                               kernels_tflops=wl.matmul_flops() / ((ktx["fwd"] + ktx["bwd_all"]) * 1e-3) / 1e12,
+                               kernels_hbm_frac=wl.algorithmic_bytes() / ((ktx["fwd"] + ktx["bwd_all"]) * 1e-3) / 1e9
+                               / peaks["hbm_gbs"])
+            del tx
+            torch.cuda.empty_cache()
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(w)
+
+    line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype=w.dtype,
+                data="synthetic",
+                config=dict(workload=w.name, images_per_gpu=w.batch, windows_per_image=w.nw, heads=w.heads, n=w.n,
+                            head_dim=w.head_dim, window_heads_per_gpu=w.units,
+                            l2="256 MiB buffer rewritten before every timed step",
+                            api="flash_win_attn_v2_func + torch.autograd.grad"),
+                frac_bf16_peak=value / world / peaks["bf16_tflops"],
+                hbm_frac_step=w.algorithmic_bytes() / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                roofline=roofline, cpu_baseline=cpu,
+                e2e=dict(value=e2e_val, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=ms_e2e),
+                gpu_launches=((5 if world > 1 else 4) * (args.steps + max(args.warmup, 3))),
+                gpu_launches_per_step=(5 if world > 1 else 4), clocks=clocks.summary(), extra=extra)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

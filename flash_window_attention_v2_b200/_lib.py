@@ -35,6 +35,7 @@ class FwdArgs(C.Structure):
         ("bias", C.c_void_p), ("mask", C.c_void_p),
         ("bias_row_stride", C.c_int64), ("mask_row_stride", C.c_int64),
         ("status", C.c_void_p), ("variant", C.c_int32), ("max_ctas", C.c_int32),
+        ("trace", C.c_void_p), ("trace_entries", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 
@@ -52,12 +53,13 @@ class BwdArgs(C.Structure):
         ("dbias", C.c_void_p), ("dscale", C.c_void_p), ("partial_out", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p), ("variant", C.c_int32), ("max_ctas", C.c_int32),
+        ("trace", C.c_void_p), ("trace_entries", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 
 EXPORTS = ("fwa2_abi_version", "fwa2_strerror", "fwa2_last_cuda_error", "fwa2_forward",
            "fwa2_bwd_workspace_bytes", "fwa2_backward", "fwa2_finalize_grads",
-           "fwa2_selftest_mma")
+           "fwa2_selftest_mma", "fwa2_selftest_mma_timing")
 
 
 def nvcc_command(out_path: str = LIB_PATH, verbose: bool = False):
@@ -113,6 +115,9 @@ def lib() -> C.CDLL:
         L.fwa2_selftest_mma.restype = C.c_int
         L.fwa2_selftest_mma.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_void_p, C.c_void_p]
+        L.fwa2_selftest_mma_timing.restype = C.c_int
+        L.fwa2_selftest_mma_timing.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                               C.c_void_p]
         if L.fwa2_abi_version() != FWA2_ABI_VERSION:
             raise RuntimeError("libfwa2_b200.so ABI version mismatch; rebuild it")
         _lib = L

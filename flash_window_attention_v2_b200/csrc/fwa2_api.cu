@@ -226,9 +226,11 @@ extern "C" int fwa2_forward(const fwa2_fwd_args* a, void* stream) {
   const int units = a->bw * a->heads;
   p.n_jobs = p.pair_mode ? (units + 1) / 2 : units;
   p.status = static_cast<DeviceStatus*>(a->status);
+  p.trace.buf = reinterpret_cast<unsigned long long*>(a->trace);
+  p.trace.cap = a->trace != nullptr ? a->trace_entries : 0;
 
   // ---- shared memory layout: prefer two CTAs per SM ----
-  const bool p_in_tmem = a->variant != 1;
+  const bool p_in_tmem = (a->variant & FWA2_FWD_P_IN_SMEM) == 0;
   const uint32_t rows_kv = p.pair_mode ? 128u : static_cast<uint32_t>((a->n + 63) / 64) * 64u;
   p.kv_stage_bytes = 2u * rows_kv * kRowBytes;
   const uint32_t p_bytes = p_in_tmem ? 0u : (p.pair_mode ? 32768u : 16384u);
@@ -313,10 +315,13 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   void* bias_t = ws + pl.off_bias_t;
   void* mask_t = ws + pl.off_mask_t;
 
-  cudaError_t e = launch_transpose_tables(a->bias, a->bias_row_stride, bias_t, a->mask,
-                                          a->mask_row_stride, mask_t, has_bias ? a->heads : 0,
-                                          has_mask ? a->n_windows : 0, a->n, pl.table_pitch, stream);
-  if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
+  cudaError_t e = cudaSuccess;
+  if ((a->variant & FWA2_BWD_SKIP_TABLES) == 0) {
+    e = launch_transpose_tables(a->bias, a->bias_row_stride, bias_t, a->mask, a->mask_row_stride,
+                                mask_t, has_bias ? a->heads : 0, has_mask ? a->n_windows : 0, a->n,
+                                pl.table_pitch, stream);
+    if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
+  }
 
   BwdParams p;
   std::memset(&p, 0, sizeof(p));
@@ -348,6 +353,8 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   p.pair_mode = pl.pair;
   p.nslots = pl.nslots;
   p.status = static_cast<DeviceStatus*>(a->status);
+  p.trace.buf = reinterpret_cast<unsigned long long*>(a->trace);
+  p.trace.cap = a->trace != nullptr ? a->trace_entries : 0;
 
   // ---- shared memory layout (one CTA per SM) ----
   p.rows_kv = pl.pair ? 128 : ((a->n + 127) / 128) * 128;
@@ -381,7 +388,7 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   e = launch_bwd(p, a->dtype == FWA2_BF16, pl.grid, stream);
   if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
 
-  if (has_bias || a->scale_is_tensor) {
+  if ((has_bias || a->scale_is_tensor) && (a->variant & FWA2_BWD_SKIP_REDUCE) == 0) {
     ReduceParams r;
     std::memset(&r, 0, sizeof(r));
     r.db_partial = p.db_partial;

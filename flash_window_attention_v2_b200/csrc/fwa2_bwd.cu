@@ -173,21 +173,36 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   const uint32_t tm_dpt = tmem + lane_base + wg * 128u + kTmDPT;
 
   // ---- K of a job: normalise in place, remember 1 / |k| ----
-  auto prologue_job = [&](uint32_t jtn) -> bool {
-    const uint32_t kvs = jtn % NKV;
+  auto prologue_job = [&](const Ring& r) -> bool {
+    const uint32_t kvs = r.stage;
     const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
-    if (!mbar_wait(bar(kbKvFull + kvs), (jtn / NKV) & 1u, ctx, 50)) return false;
+    if (!mbar_wait(bar(kbKvFull + kvs), r.phase, ctx, 50)) return false;
     for (uint32_t rr = tid; rr < static_cast<uint32_t>(p.rows_kv); rr += 256u)
       rk_arr[kvs * p.rows_kv + rr] = normalise_row<T>(k_base, rr);
     fence_proxy_async_smem();
     mbar_arrive(bar(kbKvReady + kvs));
     return true;
   };
+  // ---- O row of a query (warpgroup 1 only): issued one tile ahead of its use so that the global
+  // load latency is hidden behind a whole step of compute ----
+  auto load_o_row = [&](const TileIt& it, uint4 (&dst)[4], float& lse_out) {
+    if (wg == 1) {
+      const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
+      const int bw = bwd_bw(p, g, it.t, m);
+      const int ig = g.pair ? static_cast<int>(lt & 63u) : it.i * kTileRows + static_cast<int>(lt);
+      if (bw < p.BW && ig < g.N) {
+        const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) dst[ch] = ldg_nc_v4(orow + ch * 8);
+        lse_out = __ldg(p.lse + bw * p.lse_sbw + g.h * p.lse_sh + ig);
+      }
+    }
+  };
   // ---- Q / dO of a query tile: warpgroup 0 normalises Q, warpgroup 1 computes delta and lse ----
-  auto prologue_tile = [&](const TileIt& it, uint32_t tqn) -> bool {
-    const uint32_t qs = tqn % kNumQdoStages;
+  auto prologue_tile = [&](const TileIt& it, const Ring& r, const uint4 (&o_row)[4], float lse) -> bool {
+    const uint32_t qs = r.stage;
     const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
-    if (!mbar_wait(bar(kbQdoFull + qs), (tqn / kNumQdoStages) & 1u, ctx, 51)) return false;
+    if (!mbar_wait(bar(kbQdoFull + qs), r.phase, ctx, 51)) return false;
     if (wg == 0) {
       normalise_row<T>(q_base, lt);
       fence_proxy_async_smem();
@@ -197,20 +212,19 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       const int ig = g.pair ? static_cast<int>(lt & 63u) : it.i * kTileRows + static_cast<int>(lt);
       float l2 = INFINITY, dl = 0.f;
       if (bw < p.BW && ig < g.N) {
-        const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
+        float dlp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t wd[4];
           lds128(q_base + 2u * kBoxBytes + sw64_offset(lt, ch), wd);
-          const uint4 ov = ldg_nc_v4(orow + ch * 8);
-          const uint32_t wo[4] = {ov.x, ov.y, ov.z, ov.w};
+          const uint32_t wo[4] = {o_row[ch].x, o_row[ch].y, o_row[ch].z, o_row[ch].w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            dl = fmaf(Elem<T>::lo(wd[i]), Elem<T>::lo(wo[i]), dl);
-            dl = fmaf(Elem<T>::hi(wd[i]), Elem<T>::hi(wo[i]), dl);
+            dlp[ch] = fmaf(Elem<T>::lo(wd[i]), Elem<T>::lo(wo[i]), dlp[ch]);
+            dlp[ch] = fmaf(Elem<T>::hi(wd[i]), Elem<T>::hi(wo[i]), dlp[ch]);
           }
         }
-        const float lse = p.lse[bw * p.lse_sbw + g.h * p.lse_sh + ig];
+        dl = (dlp[0] + dlp[1]) + (dlp[2] + dlp[3]);
         l2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
       }
       rowstats[qs * 256u + lt] = l2;
@@ -220,10 +234,19 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     return true;
   };
 
-  uint32_t jt = 0, tq = 0, nst = 0, cbm = 0, kdkv = 0, kdq = 0;
+  uint32_t jt = 0, nst = 0, kdkv = 0, kdq = 0;
+  Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS), bm_ring(NBM);
+  TraceCursor tr = (lt == 0) ? trace_begin(p.trace, wg == 0 ? 0 : 3) : TraceCursor{nullptr, 0};
   TileIt cur{0, 0, 0};
-  if (!prologue_job(0)) return;
-  if (!prologue_tile(cur, 0)) return;
+  uint4 o_row[4] = {};
+  float lse_pf = 0.f;
+  load_o_row(cur, o_row, lse_pf);
+  if (!prologue_job(kv_ring)) return;
+  if (!prologue_tile(cur, qdo_ring, o_row, lse_pf)) return;
+  {
+    TileIt t1 = cur;
+    if (tile_next(g, t1)) load_o_row(t1, o_row, lse_pf);
+  }
 
   while (true) {
     TileIt nxt = cur;
@@ -231,20 +254,27 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     // With two K/V stages the next job's K is normalised one tile ahead of its first use; with a
     // single stage its load can only start once this job is finished, so it is done at the end.
     bool defer_job = false;
+    trace_ev(tr, 1);
+    Ring kv_next = kv_ring, qdo_next = qdo_ring;
+    kv_next.advance();
+    qdo_next.advance();
     if (has_next) {
       if (nxt.t != cur.t) {
         if (NKV >= 2) {
-          if (!prologue_job(jt + 1)) return;
+          if (!prologue_job(kv_next)) return;
         } else {
           defer_job = true;
         }
       }
-      if (!prologue_tile(nxt, tq + 1)) return;
+      if (!prologue_tile(nxt, qdo_next, o_row, lse_pf)) return;
+      TileIt nxt2 = nxt;
+      if (tile_next(g, nxt2)) load_o_row(nxt2, o_row, lse_pf);
     }
 
+    trace_ev(tr, 2);
     // ------------------------------ my step of the current tile ------------------------------
     const int nr = step_rows(g, cur.i, static_cast<int>(wg));
-    const uint32_t kvs = jt % NKV;
+    const uint32_t kvs = kv_ring.stage;
     if (nr > 0) {
       bool key_ok;
       int jg;
@@ -258,11 +288,13 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
         key_ok = jg < g.N;
       }
       if (!mbar_wait(bar(kbStFull + wg), nst & 1u, ctx, 52)) return;
-      const uint32_t dsb = tq % NDS;
-      if (!mbar_wait(bar(kbDsFree + dsb), ((tq / NDS) & 1u) ^ 1u, ctx, 53)) return;
+      trace_ev(tr, 3);
+      const uint32_t dsb = ds_ring.stage;
+      if (!mbar_wait(bar(kbDsFree + dsb), ds_ring.phase ^ 1u, ctx, 53)) return;
       tc_fence_after();
+      trace_ev(tr, 4);
       const uint32_t ds_slab = smem_base + p.off_ds + dsb * kDsTileBytes + wg * 16384u;
-      const uint32_t qs = tq % kNumQdoStages;
+      const uint32_t qs = qdo_ring.stage;
       const float* lse2 = rowstats + qs * 256u + wg * 64u;
       const float* delta = rowstats + qs * 256u + 128u + wg * 64u;
       const long long db_buf = g.pair ? 2ll * blockIdx.x + wg : static_cast<long long>(blockIdx.x);
@@ -281,13 +313,15 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           tmem_ld32(tm_st + 32u * c, sv);
           tmem_ld32(tm_dpt + 32u * c, dpv);
           tmem_wait_ld();
+          trace_ev(tr, 5);
           uint32_t bias_tile = 0, mask_tile = 0;
-          const uint32_t st = cbm % NBM;
+          const uint32_t st = bm_ring.stage;
           if (any_table) {
             bias_tile = smem_base + p.off_bm + (wg * NBM + st) * (2u * kTableTileBytes);
             mask_tile = bias_tile + kTableTileBytes;
-            if (!mbar_wait(bar(kbBmFull + 2 * wg + st), (cbm / NBM) & 1u, ctx, 54)) return;
+            if (!mbar_wait(bar(kbBmFull + 2 * wg + st), bm_ring.phase, ctx, 54)) return;
           }
+          trace_ev(tr, 6);
           float* dbp = db_row != nullptr ? db_row + kChunkCols * c : nullptr;
           if (rows_left >= kChunkCols)
             bwd_chunk<T, false>(p.has_bias, p.has_mask, sv, dpv, bias_tile, mask_tile, lt,
@@ -295,9 +329,10 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           else
             bwd_chunk<T, true>(p.has_bias, p.has_mask, sv, dpv, bias_tile, mask_tile, lt,
                                lse2 + 32 * c, delta + 32 * c, scale, rows_left, dbp, db_store, pw, dw);
+          trace_ev(tr, 7);
           if (any_table) {
             mbar_arrive(bar(kbBmFree + 2 * wg + st));
-            ++cbm;
+            bm_ring.advance();
           }
           if (!key_ok) {
 #pragma unroll
@@ -314,12 +349,14 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           const uint32_t w4[4] = {dw[qd * 4], dw[qd * 4 + 1], dw[qd * 4 + 2], dw[qd * 4 + 3]};
           sts128(ds_slab + sw128_offset(lt, 4u * c + qd), w4);
         }
+        trace_ev(tr, 8);
       }
       tmem_wait_st();
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(bar(kbPtFull + wg));
       ++nst;
+      trace_ev(tr, 9);
     }
 
     // ------------------------------ epilogues ------------------------------
@@ -328,6 +365,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       if (!mbar_wait(bar(kbDkvFull), kdkv & 1u, ctx, 55)) return;
       ++kdkv;
       tc_fence_after();
+      trace_ev(tr, 10);
       const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
       const int bw = bwd_bw(p, g, cur.t, m);
       const int jg = g.pair ? static_cast<int>(lt & 63u) : cur.j * kTileRows + static_cast<int>(lt);
@@ -387,12 +425,14 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
         }
       }
       if (cur.j == g.KB - 1) mbar_arrive(bar(kbKvFree + kvs));   // K^ in shared memory no longer needed
+      trace_ev(tr, 11);
 
       if (cur.j == g.KB - 1) {
         // dQ of every query tile of the job is complete
         if (!mbar_wait(bar(kbDqFull), kdq & 1u, ctx, 56)) return;
         ++kdq;
         tc_fence_after();
+        trace_ev(tr, 12);
         for (int i = static_cast<int>(wg); i < g.MT; i += 2) {
           const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
           const int bwq = bwd_bw(p, g, cur.t, mq);
@@ -444,15 +484,20 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
         }
         tc_fence_before();
         mbar_arrive(bar(kbDqFree));
+        trace_ev(tr, 13);
       }
     }
 
     if (!has_next) break;
     if (defer_job) {
-      if (!prologue_job(jt + 1)) return;
+      if (!prologue_job(kv_next)) return;
     }
-    if (nxt.t != cur.t) ++jt;
-    ++tq;
+    if (nxt.t != cur.t) {
+      ++jt;
+      kv_ring = kv_next;
+    }
+    qdo_ring = qdo_next;
+    ds_ring.advance();
     cur = nxt;
   }
 }
@@ -470,53 +515,65 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
   const uint32_t NKV = p.n_kv_stages, NDS = p.n_ds_bufs;
   const uint32_t idesc_acc = make_idesc(fmt, 128, 32, 0, 1);   // A in TMEM, B MN-major
   const uint32_t idesc_dq = make_idesc(fmt, 128, 32, 1, 1);    // A and B MN-major
+  // descriptor templates: only the start-address field changes from one MMA to the next
+  const DescBase dk64 = make_desc_base(0, 16, 512, kSw64);      // K-major rows of 64 bytes
+  const DescBase dm64 = make_desc_base(0, 512, 512, kSw64);     // MN-major rows of 64 bytes
+  const DescBase dds = make_desc_base(0, 16384, 1024, kSw128);  // dS tile, MN-major, two slabs
 
-  auto stage_bases = [&](uint32_t jtn, uint32_t tqn, uint32_t& k_base, uint32_t& v_base,
-                         uint32_t& q_base, uint32_t& do_base) {
-    k_base = smem_base + p.off_kv + (jtn % NKV) * p.kv_stage_bytes;
-    v_base = k_base + static_cast<uint32_t>(p.rows_kv) * kRowBytes;
-    q_base = smem_base + p.off_qdo + (tqn % kNumQdoStages) * kQdoStageBytes;
-    do_base = q_base + 2u * kBoxBytes;
+  struct Bases {
+    uint32_t k, v, q, dO;
+  };
+  auto stage_bases = [&](const Ring& kv, const Ring& qdo) {
+    Bases b;
+    b.k = smem_base + p.off_kv + kv.stage * p.kv_stage_bytes;
+    b.v = b.k + static_cast<uint32_t>(p.rows_kv) * kRowBytes;
+    b.q = smem_base + p.off_qdo + qdo.stage * kQdoStageBytes;
+    b.dO = b.q + 2u * kBoxBytes;
+    return b;
   };
   // S^T = K^ Q^^T and dP^T = V dO^T for step w of a tile
-  auto issue_sdp = [&](const TileIt& it, int w, uint32_t jtn, uint32_t tqn) {
+  auto issue_sdp = [&](const TileIt& it, int w, const Bases& b) {
     const int nr = step_rows(g, it.i, w);
     const uint32_t n16 = static_cast<uint32_t>(min(kStepCols, ((nr + 15) / 16) * 16));
-    uint32_t k_base, v_base, q_base, do_base;
-    stage_bases(jtn, tqn, k_base, v_base, q_base, do_base);
-    const uint32_t key_off = g.pair ? 0u : static_cast<uint32_t>(it.j) * kTileRows * kRowBytes;
-    const uint32_t row_off = static_cast<uint32_t>(w) * kStepCols * kRowBytes;
+    const uint32_t key_off = g.pair ? 0u : static_cast<uint32_t>(it.j) * (kTileRows * kRowBytes);
+    const uint32_t row_off = static_cast<uint32_t>(w) * (kStepCols * kRowBytes);
     const uint32_t idesc = make_idesc(fmt, 128, n16, 0, 0);
-#pragma unroll
-    for (uint32_t k = 0; k < 2; ++k)
-      mma_ss(tmem + w * 128u + kTmST, make_smem_desc(k_base + key_off + k * 32u, 16, 512, kSw64),
-             make_smem_desc(q_base + row_off + k * 32u, 16, 512, kSw64), idesc, k);
-#pragma unroll
-    for (uint32_t k = 0; k < 2; ++k)
-      mma_ss(tmem + w * 128u + kTmDPT, make_smem_desc(v_base + key_off + k * 32u, 16, 512, kSw64),
-             make_smem_desc(do_base + row_off + k * 32u, 16, 512, kSw64), idesc, k);
+    const uint32_t st = tmem + w * 128u + kTmST, dpt = tmem + w * 128u + kTmDPT;
+    // the two accumulation chains are interleaved: back-to-back MMAs into one accumulator wait
+    // for each other
+    mma_ss(st, desc_at(dk64, b.k + key_off), desc_at(dk64, b.q + row_off), idesc, 0u);
+    mma_ss(dpt, desc_at(dk64, b.v + key_off), desc_at(dk64, b.dO + row_off), idesc, 0u);
+    mma_ss(st, desc_at(dk64, b.k + key_off + 32u), desc_at(dk64, b.q + row_off + 32u), idesc, 1u);
+    mma_ss(dpt, desc_at(dk64, b.v + key_off + 32u), desc_at(dk64, b.dO + row_off + 32u), idesc, 1u);
     mma_commit(bar(kbStFull + w));
   };
 
-  uint32_t jt = 0, tq = 0, kdkv = 0, kdq = 0;
+  uint32_t kdkv = 0, kdq = 0;
+  TraceCursor tr = trace_begin(p.trace, 1);
   uint32_t nst[2] = {0u, 0u};
+  Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS);
   TileIt cur{0, 0, 0};
   if (!mbar_wait(bar(kbKvReady + 0), 0u, ctx, 60)) return;
   if (!mbar_wait(bar(kbQdoReady + 0), 0u, ctx, 61)) return;
   tc_fence_after();
-  for (int w = 0; w < 2; ++w)
-    if (step_rows(g, cur.i, w) > 0) issue_sdp(cur, w, 0, 0);
+  {
+    const Bases b0 = stage_bases(kv_ring, qdo_ring);
+    for (int w = 0; w < 2; ++w)
+      if (step_rows(g, cur.i, w) > 0) issue_sdp(cur, w, b0);
+  }
 
   while (true) {
     TileIt nxt = cur;
     const bool has_next = tile_next(g, nxt);
     const bool cross = has_next && nxt.t != cur.t;
-    const uint32_t jt_next = cross ? jt + 1 : jt;
+    Ring kv_next = kv_ring, qdo_next = qdo_ring;
+    if (cross) kv_next.advance();
+    qdo_next.advance();
     // Scores of the next tile are issued right behind this tile's dV / dK products, except across
     // a job boundary when K of the next job cannot be ready yet (single K/V stage).
     const bool look_now = has_next && !(cross && NKV < 2);
-    uint32_t k_base, v_base, q_base, do_base;
-    stage_bases(jt, tq, k_base, v_base, q_base, do_base);
+    const Bases b = stage_bases(kv_ring, qdo_ring);
+    const Bases bn = stage_bases(kv_next, qdo_next);
 
     if (cur.i == 0) {
       // the previous key block's dK / dV must have been read out before they are overwritten
@@ -530,65 +587,62 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
         if (!mbar_wait(bar(kbPtFull + w), nst[w] & 1u, ctx, 64)) return;
         ++nst[w];
         tc_fence_after();
-        const uint32_t row_off = static_cast<uint32_t>(w) * kStepCols * kRowBytes;
+        trace_ev(tr, 30 + w);
+        const uint32_t row_off = static_cast<uint32_t>(w) * (kStepCols * kRowBytes);
+        const uint32_t first = (cur.i > 0 || w > 0) ? 1u : 0u;
+        const uint32_t a_p = tmem + w * 128u + kTmST, a_ds = tmem + w * 128u + kTmDPT;
 #pragma unroll
         for (uint32_t k = 0; k < 4; ++k) {
-          const uint32_t acc = (cur.i > 0 || w > 0 || k > 0) ? 1u : 0u;
-          mma_ts(tmem + kTmDV, tmem + w * 128u + kTmST + k * 8u,
-                 make_smem_desc(do_base + row_off + k * 1024u, 512, 512, kSw64), idesc_acc, acc);
-        }
-#pragma unroll
-        for (uint32_t k = 0; k < 4; ++k) {
-          const uint32_t acc = (cur.i > 0 || w > 0 || k > 0) ? 1u : 0u;
-          mma_ts(tmem + kTmDK, tmem + w * 128u + kTmDPT + k * 8u,
-                 make_smem_desc(q_base + row_off + k * 1024u, 512, 512, kSw64), idesc_acc, acc);
+          mma_ts(tmem + kTmDV, a_p + k * 8u, desc_at(dm64, b.dO + row_off + k * 1024u), idesc_acc, first | k);
+          mma_ts(tmem + kTmDK, a_ds + k * 8u, desc_at(dm64, b.q + row_off + k * 1024u), idesc_acc, first | k);
         }
       }
+      trace_ev(tr, 32 + w);
       if (look_now) {
         if (w == 0) {
           if (cross) {
-            if (!mbar_wait(bar(kbKvReady + jt_next % NKV), (jt_next / NKV) & 1u, ctx, 65)) return;
+            if (!mbar_wait(bar(kbKvReady + kv_next.stage), kv_next.phase, ctx, 65)) return;
           }
-          const uint32_t tqn = tq + 1;
-          if (!mbar_wait(bar(kbQdoReady + tqn % kNumQdoStages), (tqn / kNumQdoStages) & 1u, ctx, 66)) return;
+          if (!mbar_wait(bar(kbQdoReady + qdo_next.stage), qdo_next.phase, ctx, 66)) return;
           tc_fence_after();
         }
-        if (step_rows(g, nxt.i, w) > 0) issue_sdp(nxt, w, jt_next, tq + 1);
+        if (step_rows(g, nxt.i, w) > 0) issue_sdp(nxt, w, bn);
+        trace_ev(tr, 34 + w);
       }
     }
     // dQ^ of query tile cur.i += dS K^ (key block cur.j)
     {
-      const uint32_t ds_base = smem_base + p.off_ds + (tq % NDS) * kDsTileBytes;
-      const uint32_t key_off = g.pair ? 0u : static_cast<uint32_t>(cur.j) * kTileRows * kRowBytes;
+      const uint32_t ds_base = smem_base + p.off_ds + ds_ring.stage * kDsTileBytes;
+      const uint32_t kb = b.k + (g.pair ? 0u : static_cast<uint32_t>(cur.j) * (kTileRows * kRowBytes));
+      const uint32_t dq_col = tmem + kTmDQ + 32u * cur.i;
+      const uint32_t first = cur.j > 0 ? 1u : 0u;
 #pragma unroll
-      for (uint32_t k = 0; k < 8; ++k) {
-        const uint32_t acc = (cur.j > 0 || k > 0) ? 1u : 0u;
-        mma_ss(tmem + kTmDQ + 32u * cur.i, make_smem_desc(ds_base + k * 2048u, 16384, 1024, kSw128),
-               make_smem_desc(k_base + key_off + k * 1024u, 512, 512, kSw64), idesc_dq, acc);
-      }
+      for (uint32_t k = 0; k < 8; ++k)
+        mma_ss(dq_col, desc_at(dds, ds_base + k * 2048u), desc_at(dm64, kb + k * 1024u), idesc_dq, first | k);
     }
-    mma_commit(bar(kbDsFree + tq % NDS));
-    mma_commit(bar(kbQdoFree + tq % kNumQdoStages));
+    mma_commit(bar(kbDsFree + ds_ring.stage));
+    mma_commit(bar(kbQdoFree + qdo_ring.stage));
+    trace_ev(tr, 36);
     if (cur.i == g.MT - 1) {
       mma_commit(bar(kbDkvFull));
       ++kdkv;
       if (cur.j == g.KB - 1) {
         mma_commit(bar(kbDqFull));
         ++kdq;
-        mma_commit(bar(kbKvFree + jt % NKV));
+        mma_commit(bar(kbKvFree + kv_ring.stage));
       }
     }
     if (!has_next) break;
     if (!look_now) {
-      if (!mbar_wait(bar(kbKvReady + jt_next % NKV), (jt_next / NKV) & 1u, ctx, 67)) return;
-      const uint32_t tqn = tq + 1;
-      if (!mbar_wait(bar(kbQdoReady + tqn % kNumQdoStages), (tqn / kNumQdoStages) & 1u, ctx, 68)) return;
+      if (!mbar_wait(bar(kbKvReady + kv_next.stage), kv_next.phase, ctx, 67)) return;
+      if (!mbar_wait(bar(kbQdoReady + qdo_next.stage), qdo_next.phase, ctx, 68)) return;
       tc_fence_after();
       for (int w = 0; w < 2; ++w)
-        if (step_rows(g, nxt.i, w) > 0) issue_sdp(nxt, w, jt_next, tq + 1);
+        if (step_rows(g, nxt.i, w) > 0) issue_sdp(nxt, w, bn);
     }
-    jt = jt_next;
-    ++tq;
+    kv_ring = kv_next;
+    qdo_ring = qdo_next;
+    ds_ring.advance();
     cur = nxt;
   }
 }
@@ -601,7 +655,7 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
 struct BmCursor {
   TileIt it;
   int c;
-  uint32_t cc;
+  uint32_t stage, phase;
   bool done;
 };
 
@@ -617,7 +671,7 @@ __device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t b
   // stream (a)
   TileIt a_it{0, 0, 0};
   bool a_kv_pending = true, a_done = false;
-  uint32_t a_jt = 0, a_tq = 0;
+  Ring a_kv(NKV), a_qdo(kNumQdoStages);
   // streams (b0), (b1)
   BmCursor bc[2];
   auto bm_seek = [&](BmCursor& b, int w) {
@@ -633,7 +687,8 @@ __device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t b
   for (int w = 0; w < 2; ++w) {
     bc[w].it = TileIt{0, 0, 0};
     bc[w].c = 0;
-    bc[w].cc = 0;
+    bc[w].stage = 0;
+    bc[w].phase = 0;
     bc[w].done = !any_table;
     if (!bc[w].done) bm_seek(bc[w], w);
   }
@@ -644,8 +699,8 @@ __device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t b
     bool progress = false;
     if (!a_done) {
       if (a_kv_pending) {
-        const uint32_t kvs = a_jt % NKV;
-        if (mbar_try_wait(bar(kbKvFree + kvs), ((a_jt / NKV) & 1u) ^ 1u)) {
+        const uint32_t kvs = a_kv.stage;
+        if (mbar_test_wait(bar(kbKvFree + kvs), a_kv.phase ^ 1u)) {
           const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
           const uint32_t v_base = k_base + static_cast<uint32_t>(p.rows_kv) * kRowBytes;
           const uint32_t full = bar(kbKvFull + kvs);
@@ -661,8 +716,8 @@ __device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t b
           progress = true;
         }
       } else {
-        const uint32_t qs = a_tq % kNumQdoStages;
-        if (mbar_try_wait(bar(kbQdoFree + qs), ((a_tq / kNumQdoStages) & 1u) ^ 1u)) {
+        const uint32_t qs = a_qdo.stage;
+        if (mbar_test_wait(bar(kbQdoFree + qs), a_qdo.phase ^ 1u)) {
           const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
           const uint32_t full = bar(kbQdoFull + qs);
           mbar_arrive_expect_tx(full, kQdoStageBytes);
@@ -672,12 +727,12 @@ __device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t b
             tma_load_4d(q_base + b * kBoxBytes, &p.tm_q, full, 0, r0, g.h, bw);
             tma_load_4d(q_base + 2u * kBoxBytes + b * kBoxBytes, &p.tm_do, full, 0, r0, g.h, bw);
           }
-          ++a_tq;
+          a_qdo.advance();
           const int t_before = a_it.t;
           if (!tile_next(g, a_it)) {
             a_done = true;
           } else if (a_it.t != t_before) {
-            ++a_jt;
+            a_kv.advance();
             a_kv_pending = true;
           }
           progress = true;
@@ -687,8 +742,8 @@ __device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t b
     for (int w = 0; w < 2; ++w) {
       BmCursor& b = bc[w];
       if (b.done) continue;
-      const uint32_t st = b.cc % NBM;
-      if (!mbar_try_wait(bar(kbBmFree + 2 * w + st), ((b.cc / NBM) & 1u) ^ 1u)) continue;
+      const uint32_t st = b.stage;
+      if (!mbar_test_wait(bar(kbBmFree + 2 * w + st), b.phase ^ 1u)) continue;
       const uint32_t base = smem_base + p.off_bm + (w * NBM + st) * (2u * kTableTileBytes);
       const uint32_t full = bar(kbBmFull + 2 * w + st);
       if (g.pair) {
@@ -711,14 +766,19 @@ __device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t b
             tma_load_3d(base + kTableTileBytes + hb * kBoxBytes, &p.tm_maskT, full, c0, r0, bw % p.nW);
         }
       }
-      ++b.cc;
+      if (++b.stage == NBM) {
+        b.stage = 0;
+        b.phase ^= 1u;
+      }
       ++b.c;
       bm_seek(b, w);
       progress = true;
     }
     if (progress) {
       idle = 0;
-    } else if ((++idle & 0x3Fu) == 0) {
+    } else if ((++idle & 0x3Fu) != 0) {
+      __nanosleep(20);
+    } else {
       if (idle == 0x40u) t0 = clock64();
       if (*ctx.abort_flag) return;
       if (clock64() - t0 > kWaitLimitCycles) {
@@ -726,7 +786,7 @@ __device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t b
         if (ctx.status != nullptr) {
           if (atomicCAS(&ctx.status->code, 0u, (70u << 8) | kStatusTimeout) == 0u) {
             ctx.status->block = blockIdx.x;
-            ctx.status->detail = (a_tq << 16) | (bc[0].cc & 0xFFFFu);
+            ctx.status->detail = (a_qdo.stage << 16) | (bc[0].stage & 0xFFFFu);
           }
         }
         return;

@@ -24,6 +24,30 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLn100 = 4.605170185988092f;
 
+// Optional timeline of CTA 0: each role appends (clock64 << 8 | event) words to its own region.
+struct Trace {
+  unsigned long long* buf;
+  int cap;
+};
+struct TraceCursor {
+  unsigned long long* p;
+  int left;
+};
+__device__ __forceinline__ TraceCursor trace_begin(const Trace& t, int role) {
+  TraceCursor c{nullptr, 0};
+  if (t.buf != nullptr && blockIdx.x == 0) {
+    c.p = t.buf + static_cast<long long>(role) * t.cap;
+    c.left = t.cap;
+  }
+  return c;
+}
+__device__ __forceinline__ void trace_ev(TraceCursor& c, unsigned int id) {
+  if (c.left > 0) {
+    *c.p++ = (static_cast<unsigned long long>(clock64()) << 8) | id;
+    --c.left;
+  }
+}
+
 struct FwdParams {
   CUtensorMap tm_q, tm_k, tm_v;   // 4-D (d, N, H, BW), box (32, 64, 1, 1), 64-byte swizzle
   CUtensorMap tm_bias;            // 3-D (N, N, H),  box (32, 64, 1)
@@ -47,6 +71,7 @@ struct FwdParams {
   uint32_t off_ctrl;                 // mbarriers, TMEM base slot, abort flag (512 bytes)
   uint32_t smem_bytes;
   DeviceStatus* status;
+  Trace trace;
 };
 
 // Normalise one 32-element row of a 64-byte-swizzled tile in place; returns 1 / max(|x|, 1e-12).
@@ -118,6 +143,7 @@ struct BwdParams {
   uint32_t off_ctrl;
   uint32_t smem_bytes;
   DeviceStatus* status;
+  Trace trace;
 };
 
 // Second stage of the dBias / dLogitScale reduction.

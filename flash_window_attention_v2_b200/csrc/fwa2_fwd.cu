@@ -72,31 +72,36 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
     }
   }
 
-  uint32_t jt = 0, tt = 0, sc = 0, cc = 0, pvc = 0;
-  const uint32_t nsb = sh.pair ? 1u : 2u;
-  for (int job = blockIdx.x; job < p.n_jobs; job += gridDim.x, ++jt) {
+  uint32_t tt = 0, pvc = 0;
+  Ring kv_ring(p.n_kv_stages), s_ring(sh.pair ? 1u : 2u), bm_ring(p.n_bm_stages);
+  TraceCursor tr = (tid == 0) ? trace_begin(p.trace, 0) : TraceCursor{nullptr, 0};
+  for (int job = blockIdx.x; job < p.n_jobs; job += gridDim.x, kv_ring.advance()) {
     const int unit = sh.pair ? 2 * job + static_cast<int>(hf) : job;
     const bool unit_ok = unit < sh.U;
     const int bw = unit / sh.H, h = unit - bw * sh.H;
     const float scale = load_scale<T>(p.scale, p.scale_is_tensor, h);
 
     // ---- normalise the K rows of this job in place ----
-    const uint32_t kvs = jt % p.n_kv_stages;
+    const uint32_t kvs = kv_ring.stage;
     const uint32_t kv_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
-    if (!mbar_wait(bar(kBarKvFull + kvs), (jt / p.n_kv_stages) & 1u, ctx, 10)) return;
+    if (!mbar_wait(bar(kBarKvFull + kvs), kv_ring.phase, ctx, 10)) return;
+    trace_ev(tr, 1);
     for (uint32_t rr = tid; rr < static_cast<uint32_t>(sh.rows_kv); rr += 128u)
       normalise_row<T>(kv_base, rr);
     fence_proxy_async_smem();
     mbar_arrive(bar(kBarKvReady + kvs));
+    trace_ev(tr, 2);
 
     for (int mt = 0; mt < sh.MT; ++mt, ++tt) {
       // ---- normalise my Q row ----
       const uint32_t qs = tt & 1u;
       const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
       if (!mbar_wait(bar(kBarQFull + qs), (tt >> 1) & 1u, ctx, 11)) return;
+      trace_ev(tr, 3);
       normalise_row<T>(q_base, tid);
       fence_proxy_async_smem();
       mbar_arrive(bar(kBarQReady + qs));
+      trace_ev(tr, 4);
 
       const int row = sh.pair ? static_cast<int>(tid & 63u) : mt * kTileRows + static_cast<int>(tid);
       const bool row_ok = unit_ok && row < sh.N;
@@ -106,12 +111,13 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
 #pragma unroll
       for (int i = 0; i < 32; ++i) acc[i] = 0.f;
 
-      for (int s = 0; s < sh.KS; ++s, ++sc) {
+      for (int s = 0; s < sh.KS; ++s, s_ring.advance()) {
         const int ncols = sh.pair ? sh.N : min(kStepCols, sh.N - s * kStepCols);
         // ---- scores of this step out of tensor memory ----
-        const uint32_t sb = sc % nsb;
-        if (!mbar_wait(bar(kBarSFull + sb), (sc / nsb) & 1u, ctx, 12)) return;
+        const uint32_t sb = s_ring.stage;
+        if (!mbar_wait(bar(kBarSFull + sb), s_ring.phase, ctx, 12)) return;
         tc_fence_after();
+        trace_ev(tr, 10);
         float x[64];
         {
           const uint32_t col = kTmemS + (sh.pair ? hf * 64u : sb * 64u);
@@ -127,6 +133,7 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
         }
         tc_fence_before();
         mbar_arrive(bar(kBarSFree + sb));
+        trace_ev(tr, 11);
 
         // ---- x = scale * cos + bias + mask ----
         if (any_table) {
@@ -134,9 +141,9 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
 #pragma unroll
           for (int c2 = 0; c2 < 2; ++c2) {
             if (c2 < nch) {
-              const uint32_t st = cc % p.n_bm_stages;
+              const uint32_t st = bm_ring.stage;
               const uint32_t bm_base = smem_base + p.off_bm + st * (2u * kTableTileBytes);
-              if (!mbar_wait(bar(kBarBmFull + st), (cc / p.n_bm_stages) & 1u, ctx, 13)) return;
+              if (!mbar_wait(bar(kBarBmFull + st), bm_ring.phase, ctx, 13)) return;
 #pragma unroll
               for (int ch = 0; ch < 4; ++ch) {
                 uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
@@ -150,7 +157,7 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
                 }
               }
               mbar_arrive(bar(kBarBmFree + st));
-              ++cc;
+              bm_ring.advance();
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i) x[c2 * 32 + i] *= scale;
@@ -166,23 +173,33 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
             if (i >= ncols) x[i] = -INFINITY;
         }
 
+        trace_ev(tr, 12);
         // ---- online softmax ----
-        float mx = x[0];
+        // eight independent chains instead of one 64-long dependent one
+        float mxp[8];
 #pragma unroll
-        for (int i = 1; i < 64; ++i) mx = fmaxf(mx, x[i]);
+        for (int i = 0; i < 8; ++i) mxp[i] = x[i];
+#pragma unroll
+        for (int i = 8; i < 64; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], x[i]);
+        const float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])),
+                               fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
         const float m_new = fmaxf(m_run, mx);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
         const float alpha = ex2f((m_run - m_use) * kLog2e);
         const float ml2 = m_use * kLog2e;
-        float sum = 0.f;
+        float sp[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sp[i] = 0.f;
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           x[i] = ex2f(fmaf(x[i], kLog2e, -ml2));
-          sum += x[i];
+          sp[i & 7] += x[i];
         }
+        const float sum = ((sp[0] + sp[1]) + (sp[2] + sp[3])) + ((sp[4] + sp[5]) + (sp[6] + sp[7]));
         l_run = fmaf(l_run, alpha, sum);
         m_run = m_new;
 
+        trace_ev(tr, 13);
         // ---- fold the previous step's P*V into the running output ----
         if (s > 0) {
           if (!mbar_wait(bar(kBarPvDone), pvc & 1u, ctx, 14)) return;
@@ -195,6 +212,7 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
           for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha_pend, __uint_as_float(r[i]));
         }
         alpha_pend = alpha;
+        trace_ev(tr, 14);
 
         // ---- hand P to the tensor core ----
         if constexpr (kPTmem) {
@@ -221,12 +239,14 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
           tc_fence_before();
         }
         mbar_arrive(bar(kBarPFull));
+        trace_ev(tr, 15);
       }
 
       // ---- last P*V of the tile, then the epilogue ----
       if (!mbar_wait(bar(kBarPvDone), pvc & 1u, ctx, 15)) return;
       ++pvc;
       tc_fence_after();
+      trace_ev(tr, 20);
       {
         uint32_t r[32];
         tmem_ld32(tmem + lane_base + kTmemPV, r);
@@ -251,6 +271,7 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
         p.lse[bw * p.lse_sbw + h * p.lse_sh + row] =
             l_run > 0.f ? m_use + __logf(l_run) : -INFINITY;
       }
+      trace_ev(tr, 21);
     }
   }
 }
@@ -264,45 +285,46 @@ __device__ void fwd_mma_role(const FwdParams& p, uint32_t smem_base, uint32_t ba
   const FwdShape sh = fwd_shape(p);
   constexpr uint32_t fmt = Elem<T>::kFmt;
   auto bar = [&](int i) { return bars + 8u * i; };
-  const uint32_t nsb = sh.pair ? 1u : 2u;
   const uint32_t idesc_pv = make_idesc(fmt, 128, 32, 0, 1);
-  uint32_t jt = 0, tt = 0, sc = 0, pc = 0;
+  const uint32_t idesc_s_full = make_idesc(fmt, 128, sh.pair ? 128u : 64u, 0, 0);
+  // the last step of a tile may cover fewer key columns
+  const int last_cols = sh.pair ? 128 : min(kStepCols, ((sh.N - (sh.KS - 1) * kStepCols + 15) / 16) * 16);
+  const uint32_t idesc_s_last = make_idesc(fmt, 128, static_cast<uint32_t>(last_cols), 0, 0);
+  const uint32_t pv_ksteps = sh.pair ? 8u : 4u;
+  uint32_t tt = 0, pc = 0;
+  Ring kv_ring(p.n_kv_stages), s_ring(sh.pair ? 1u : 2u);
+  TraceCursor tr = trace_begin(p.trace, 1);
+  // descriptor templates: only the start-address field changes from one MMA to the next
+  const DescBase d64 = make_desc_base(0, 16, 512, kSw64);       // K-major rows of 64 bytes
+  const DescBase dv64 = make_desc_base(0, 512, 512, kSw64);     // MN-major rows of 64 bytes
+  const DescBase dp128 = make_desc_base(smem_base + p.off_p, 16, 1024, kSw128);
 
-  for (int job = blockIdx.x; job < p.n_jobs; job += gridDim.x, ++jt) {
-    const uint32_t kvs = jt % p.n_kv_stages;
+  for (int job = blockIdx.x; job < p.n_jobs; job += gridDim.x, kv_ring.advance()) {
+    const uint32_t kvs = kv_ring.stage;
     const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
     const uint32_t v_base = k_base + static_cast<uint32_t>(sh.rows_kv) * kRowBytes;
-    if (!mbar_wait(bar(kBarKvReady + kvs), (jt / p.n_kv_stages) & 1u, ctx, 20)) return;
+    if (!mbar_wait(bar(kBarKvReady + kvs), kv_ring.phase, ctx, 20)) return;
+    trace_ev(tr, 30);
 
     for (int mt = 0; mt < sh.MT; ++mt, ++tt) {
       const uint32_t qs = tt & 1u;
       const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
       if (!mbar_wait(bar(kBarQReady + qs), (tt >> 1) & 1u, ctx, 21)) return;
       tc_fence_after();
+      trace_ev(tr, 31);
 
       auto issue_scores = [&](int s) -> bool {
-        const uint32_t sb = sc % nsb;
-        if (!mbar_wait(bar(kBarSFree + sb), ((sc / nsb) & 1u) ^ 1u, ctx, 22)) return false;
+        const uint32_t sb = s_ring.stage;
+        if (!mbar_wait(bar(kBarSFree + sb), s_ring.phase ^ 1u, ctx, 22)) return false;
         tc_fence_after();
-        int ncols;
-        uint32_t kb, dcol;
-        if (sh.pair) {
-          ncols = 128;
-          kb = k_base;
-          dcol = kTmemS;
-        } else {
-          ncols = min(kStepCols, ((sh.N - s * kStepCols + 15) / 16) * 16);
-          kb = k_base + static_cast<uint32_t>(s) * kStepCols * kRowBytes;
-          dcol = kTmemS + sb * 64u;
-        }
-        const uint32_t idesc = make_idesc(fmt, 128, static_cast<uint32_t>(ncols), 0, 0);
-#pragma unroll
-        for (uint32_t k = 0; k < 2; ++k) {
-          mma_ss(tmem + dcol, make_smem_desc(q_base + k * 32u, 16, 512, kSw64),
-                 make_smem_desc(kb + k * 32u, 16, 512, kSw64), idesc, k);
-        }
+        const uint32_t kb = sh.pair ? k_base : k_base + static_cast<uint32_t>(s) * (kStepCols * kRowBytes);
+        const uint32_t dcol = tmem + kTmemS + (sh.pair ? 0u : sb * 64u);
+        const uint32_t idesc = (s == sh.KS - 1) ? idesc_s_last : idesc_s_full;
+        mma_ss(dcol, desc_at(d64, q_base), desc_at(d64, kb), idesc, 0u);
+        mma_ss(dcol, desc_at(d64, q_base + 32u), desc_at(d64, kb + 32u), idesc, 1u);
         mma_commit(bar(kBarSFull + sb));
-        ++sc;
+        s_ring.advance();
+        trace_ev(tr, 32);
         return true;
       };
 
@@ -314,18 +336,20 @@ __device__ void fwd_mma_role(const FwdParams& p, uint32_t smem_base, uint32_t ba
         if (s + 1 == sh.KS) mma_commit(bar(kBarQFree + qs));
         if (!mbar_wait(bar(kBarPFull), pc & 1u, ctx, 23)) return;
         tc_fence_after();
-        const uint32_t vb = sh.pair ? v_base : v_base + static_cast<uint32_t>(s) * kStepCols * kRowBytes;
-        const uint32_t ksteps = sh.pair ? 8u : 4u;
-        for (uint32_t k = 0; k < ksteps; ++k) {
-          const uint64_t bd = make_smem_desc(vb + k * 1024u, 512, 512, kSw64);
-          if constexpr (kPTmem) {
-            mma_ts(tmem + kTmemPV, tmem + kTmemP + k * 8u, bd, idesc_pv, k);
-          } else {
-            const uint32_t pa = smem_base + p.off_p + (k >> 2) * 16384u + (k & 3u) * 32u;
-            mma_ss(tmem + kTmemPV, make_smem_desc(pa, 16, 1024, kSw128), bd, idesc_pv, k);
-          }
+        trace_ev(tr, 33);
+        const uint32_t vb = sh.pair ? v_base : v_base + static_cast<uint32_t>(s) * (kStepCols * kRowBytes);
+        if constexpr (kPTmem) {
+#pragma unroll 4
+          for (uint32_t k = 0; k < pv_ksteps; ++k)
+            mma_ts(tmem + kTmemPV, tmem + kTmemP + k * 8u, desc_at(dv64, vb + k * 1024u), idesc_pv, k);
+        } else {
+#pragma unroll 4
+          for (uint32_t k = 0; k < pv_ksteps; ++k)
+            mma_ss(tmem + kTmemPV, desc_at(dp128, (k >> 2) * 16384u + (k & 3u) * 32u),
+                   desc_at(dv64, vb + k * 1024u), idesc_pv, k);
         }
         mma_commit(bar(kBarPvDone));
+        trace_ev(tr, 34);
       }
     }
     mma_commit(bar(kBarKvFree + kvs));
@@ -348,89 +372,89 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
 
   // stream (a): item 0 of a job is K/V, items 1..MT are the Q tiles
   int a_job = blockIdx.x, a_item = 0;
-  uint32_t a_jt = 0, a_tt = 0;
+  uint32_t a_tt = 0;
+  Ring a_kv(p.n_kv_stages), b_ring(p.n_bm_stages);
   // stream (b)
   int b_job = blockIdx.x, b_mt = 0, b_s = 0, b_c2 = 0;
-  uint32_t b_cc = 0;
   bool a_done = a_job >= p.n_jobs;
   bool b_done = !any_table || b_job >= p.n_jobs;
 
+  // (window, head, mask plane) of the one or two units of a job; recomputed when the job changes
+  struct JobUnits { int bw0, bw1, h0, h1, mw0, mw1; };
+  auto job_units = [&](int job) {
+    JobUnits u;
+    const int u0 = sh.pair ? 2 * job : job, u1 = sh.pair ? 2 * job + 1 : job;
+    u.bw0 = u0 / sh.H; u.h0 = u0 - u.bw0 * sh.H; u.mw0 = p.has_mask ? u.bw0 % p.nW : 0;
+    u.bw1 = u1 / sh.H; u.h1 = u1 - u.bw1 * sh.H; u.mw1 = p.has_mask ? u.bw1 % p.nW : 0;
+    return u;
+  };
+  JobUnits a_u = job_units(a_job), b_u = job_units(b_job);
+
   long long t0 = clock64();
   uint32_t idle = 0;
+  TraceCursor tr = trace_begin(p.trace, 2);
   while (!a_done || !b_done) {
     bool progress = false;
     if (!a_done) {
       if (a_item == 0) {
-        const uint32_t kvs = a_jt % p.n_kv_stages;
-        if (mbar_try_wait(bar(kBarKvFree + kvs), ((a_jt / p.n_kv_stages) & 1u) ^ 1u)) {
+        const uint32_t kvs = a_kv.stage;
+        if (mbar_test_wait(bar(kBarKvFree + kvs), a_kv.phase ^ 1u)) {
           const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
           const uint32_t v_base = k_base + static_cast<uint32_t>(sh.rows_kv) * kRowBytes;
           const uint32_t full = bar(kBarKvFull + kvs);
           mbar_arrive_expect_tx(full, 2u * static_cast<uint32_t>(sh.rows_kv) * kRowBytes);
           const int nbox = sh.rows_kv / kBoxRows;
           for (int b = 0; b < nbox; ++b) {
-            int bw, h, r0;
-            if (sh.pair) {
-              const int unit = 2 * a_job + b;
-              bw = unit / sh.H; h = unit - bw * sh.H; r0 = 0;
-            } else {
-              bw = a_job / sh.H; h = a_job - bw * sh.H; r0 = b * kBoxRows;
-            }
-            tma_load_4d(k_base + b * kBoxBytes, &p.tm_k, full, 0, r0, h, bw);
-            tma_load_4d(v_base + b * kBoxBytes, &p.tm_v, full, 0, r0, h, bw);
+            const int ui = sh.pair ? b : 0;
+            const int r0 = sh.pair ? 0 : b * kBoxRows;
+            tma_load_4d(k_base + b * kBoxBytes, &p.tm_k, full, 0, r0, ui ? a_u.h1 : a_u.h0, ui ? a_u.bw1 : a_u.bw0);
+            tma_load_4d(v_base + b * kBoxBytes, &p.tm_v, full, 0, r0, ui ? a_u.h1 : a_u.h0, ui ? a_u.bw1 : a_u.bw0);
           }
           a_item = 1;
           progress = true;
+          trace_ev(tr, 40);
         }
       } else {
         const uint32_t qs = a_tt & 1u;
-        if (mbar_try_wait(bar(kBarQFree + qs), ((a_tt >> 1) & 1u) ^ 1u)) {
+        if (mbar_test_wait(bar(kBarQFree + qs), ((a_tt >> 1) & 1u) ^ 1u)) {
           const int mt = a_item - 1;
           const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
           const uint32_t qfull = bar(kBarQFull + qs);
           mbar_arrive_expect_tx(qfull, 2u * kBoxBytes);
           for (int b = 0; b < 2; ++b) {
-            int bw, h, r0;
-            if (sh.pair) {
-              const int unit = 2 * a_job + b;
-              bw = unit / sh.H; h = unit - bw * sh.H; r0 = 0;
-            } else {
-              bw = a_job / sh.H; h = a_job - bw * sh.H; r0 = mt * kTileRows + b * kBoxRows;
-            }
-            tma_load_4d(q_base + b * kBoxBytes, &p.tm_q, qfull, 0, r0, h, bw);
+            const int ui = sh.pair ? b : 0;
+            const int r0 = sh.pair ? 0 : mt * kTileRows + b * kBoxRows;
+            tma_load_4d(q_base + b * kBoxBytes, &p.tm_q, qfull, 0, r0, ui ? a_u.h1 : a_u.h0, ui ? a_u.bw1 : a_u.bw0);
           }
           ++a_tt;
+          trace_ev(tr, 41);
           if (++a_item > sh.MT) {
             a_item = 0;
-            ++a_jt;
+            a_kv.advance();
             a_job += gridDim.x;
             a_done = a_job >= p.n_jobs;
+            a_u = job_units(a_job);
           }
           progress = true;
         }
       }
     }
     if (!b_done) {
-      const uint32_t st = b_cc % p.n_bm_stages;
-      if (mbar_try_wait(bar(kBarBmFree + st), ((b_cc / p.n_bm_stages) & 1u) ^ 1u)) {
+      const uint32_t st = b_ring.stage;
+      if (mbar_test_wait(bar(kBarBmFree + st), b_ring.phase ^ 1u)) {
         const uint32_t base = smem_base + p.off_bm + st * (2u * kTableTileBytes);
         const uint32_t full = bar(kBarBmFull + st);
         mbar_arrive_expect_tx(full, table_bytes);
         for (int b = 0; b < 2; ++b) {
-          int bw, h, r0, c0;
-          if (sh.pair) {
-            const int unit = 2 * b_job + b;
-            bw = unit / sh.H; h = unit - bw * sh.H; r0 = 0; c0 = b_c2 * kChunkCols;
-          } else {
-            bw = b_job / sh.H; h = b_job - bw * sh.H;
-            r0 = b_mt * kTileRows + b * kBoxRows;
-            c0 = b_s * kStepCols + b_c2 * kChunkCols;
-          }
-          if (p.has_bias) tma_load_3d(base + b * kBoxBytes, &p.tm_bias, full, c0, r0, h);
+          const int ui = sh.pair ? b : 0;
+          const int r0 = sh.pair ? 0 : b_mt * kTileRows + b * kBoxRows;
+          const int c0 = sh.pair ? b_c2 * kChunkCols : b_s * kStepCols + b_c2 * kChunkCols;
+          if (p.has_bias) tma_load_3d(base + b * kBoxBytes, &p.tm_bias, full, c0, r0, ui ? b_u.h1 : b_u.h0);
           if (p.has_mask)
-            tma_load_3d(base + kTableTileBytes + b * kBoxBytes, &p.tm_mask, full, c0, r0, bw % p.nW);
+            tma_load_3d(base + kTableTileBytes + b * kBoxBytes, &p.tm_mask, full, c0, r0, ui ? b_u.mw1 : b_u.mw0);
         }
-        ++b_cc;
+        b_ring.advance();
+        trace_ev(tr, 42);
         // advance (chunk, step, tile, job)
         const int ncols = sh.pair ? sh.N : min(kStepCols, sh.N - b_s * kStepCols);
         const int nch = ncols > kChunkCols ? 2 : 1;
@@ -442,6 +466,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
               b_mt = 0;
               b_job += gridDim.x;
               b_done = b_job >= p.n_jobs;
+              b_u = job_units(b_job);
             }
           }
         }
@@ -450,7 +475,9 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
     }
     if (progress) {
       idle = 0;
-    } else if ((++idle & 0x3Fu) == 0) {
+    } else if ((++idle & 0x3Fu) != 0) {
+      __nanosleep(20);
+    } else {
       if (idle == 0x40u) t0 = clock64();
       if (*ctx.abort_flag) return;
       if (clock64() - t0 > kWaitLimitCycles) {
@@ -458,7 +485,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
         if (ctx.status != nullptr) {
           if (atomicCAS(&ctx.status->code, 0u, (30u << 8) | kStatusTimeout) == 0u) {
             ctx.status->block = blockIdx.x;
-            ctx.status->detail = (static_cast<uint32_t>(a_item) << 16) | (b_cc & 0xFFFFu);
+            ctx.status->detail = (static_cast<uint32_t>(a_item) << 16) | (b_ring.stage & 0xFFFFu);
           }
         }
         return;

@@ -58,6 +58,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+// Non-blocking test of a phase (try_wait may suspend the thread for a while; pollers that serve
+// several queues must not).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Shared-memory abort flag + global status word, handed to every bounded wait.
 struct WaitCtx {
   volatile uint32_t* abort_flag;   // in shared memory
@@ -201,6 +217,45 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t in_fmt, uint32_t m, u
                                                   uint32_t a_mn, uint32_t b_mn) {
   return (1u << 4) | (in_fmt << 7) | (in_fmt << 10) | (a_mn << 15) | (b_mn << 16) |
          ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// A descriptor whose start address can be advanced with one 32-bit add (the address field sits in
+// the low word and never carries out of its 14 bits for addresses below 256 KiB).
+struct DescBase {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ DescBase make_desc_base(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes, SmemSwizzle sw) {
+  const uint64_t d = make_smem_desc(smem_addr, lbo_bytes, sbo_bytes, sw);
+  return DescBase{static_cast<uint32_t>(d), static_cast<uint32_t>(d >> 32)};
+}
+__device__ __forceinline__ uint64_t desc_at(const DescBase& b, uint32_t byte_offset) {
+  return (static_cast<uint64_t>(b.hi) << 32) | static_cast<uint64_t>(b.lo + (byte_offset >> 4));
+}
+
+// Position in a ring of `n` pipeline stages with the mbarrier phase bit that goes with it.
+struct Ring {
+  uint32_t stage, phase, n;
+  __device__ __forceinline__ explicit Ring(uint32_t n_) : stage(0), phase(0), n(n_) {}
+  __device__ __forceinline__ void advance() {
+    if (++stage == n) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
+// One lane of a fully converged warp (the same lane every time).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "elect.sync _|P, 0xFFFFFFFF;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // D[tmem] (+)= A[smem] * B[smem].  Issued by one thread.

@@ -151,7 +151,111 @@ selftest_kernel(int mode, const uint16_t* __restrict__ a, const uint16_t* __rest
   if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
+// Issue / completion cost of short tcgen05.mma sequences (kind::f16, M = 128, K = 16 each).
+//   n:        N of every MMA
+//   a_tmem:   1 = A operand from tensor memory, 0 = from shared memory
+//   chains:   1, 2 or 4 independent accumulators the sequence alternates between (one thread
+//             issues); 8 = the whole warp runs the loop and an elected lane issues
+//   count:    MMAs in the sequence
+// out[0] = cycles to issue the sequence, out[1] = cycles until the commit barrier fires.
+__global__ void __launch_bounds__(128, 1)
+mma_timing_kernel(int n, int a_tmem, int chains, int count, float* __restrict__ out,
+                  DeviceStatus* status) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // zero the operand area so that the arithmetic is well defined
+  for (uint32_t i = tid; i < (65536u + 1024u) / 16u; i += 128) {
+    const uint32_t z[4] = {0u, 0u, 0u, 0u};
+    if (smem_u32(smem_raw) + i * 16u + 16u <= base + 65536u) sts128(smem_u32(smem_raw) + i * 16u, z);
+  }
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_base_slot), 512);
+    tmem_relinquish();
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+  long long t0 = 0, t1 = 0;
+  const bool uniform_style = chains >= 8;   // chains = 8: whole warp runs the loop, one elected lane issues
+  if (uniform_style) {
+    if (warp == 0) {
+      const uint32_t idesc = make_idesc(1, 128, static_cast<uint32_t>(n), 0, 0);
+      const DescBase db = make_desc_base(base + 32768u, 16, 512, kSw64);
+      const DescBase da = make_desc_base(base, 16, 512, kSw64);
+      t0 = clock64();
+#pragma unroll 8
+      for (int i = 0; i < count; ++i) {
+        const uint64_t bd = desc_at(db, (i & 1) * 32u);
+        const uint64_t ad = desc_at(da, (i & 1) * 32u);
+        const uint32_t d = tmem + (static_cast<uint32_t>(i) & 1u) * 64u;
+        if (elect_one()) {
+          if (a_tmem) mma_ts(d, tmem + 256u + (i & 3) * 8u, bd, idesc, i > 1);
+          else mma_ss(d, ad, bd, idesc, i > 1);
+        }
+        __syncwarp();
+      }
+      t1 = clock64();
+      if (elect_one()) mma_commit(smem_u32(&bar));
+      __syncwarp();
+    }
+  } else if (tid == 0) {
+    const uint32_t idesc = make_idesc(1, 128, static_cast<uint32_t>(n), 0, 0);
+    const DescBase da = make_desc_base(base, 16, 512, kSw64);
+    const DescBase db = make_desc_base(base + 32768u, 16, 512, kSw64);
+    const uint32_t cmask = static_cast<uint32_t>(chains) - 1u;   // chains is 1, 2 or 4
+    t0 = clock64();
+    if (a_tmem) {
+#pragma unroll 8
+      for (int i = 0; i < count; ++i)
+        mma_ts(tmem + (static_cast<uint32_t>(i) & cmask) * 64u, tmem + 256u + (i & 3) * 8u,
+               desc_at(db, (i & 1) * 32u), idesc, static_cast<uint32_t>(i) > cmask);
+    } else {
+#pragma unroll 8
+      for (int i = 0; i < count; ++i)
+        mma_ss(tmem + (static_cast<uint32_t>(i) & cmask) * 64u, desc_at(da, (i & 1) * 32u),
+               desc_at(db, (i & 1) * 32u), idesc, static_cast<uint32_t>(i) > cmask);
+    }
+    t1 = clock64();
+    mma_commit(smem_u32(&bar));
+  }
+  WaitCtx ctx{&abort_flag, status};
+  mbar_wait(smem_u32(&bar), 0, ctx, 2);
+  if (tid == 0) {
+    const long long t2 = clock64();
+    out[0] = static_cast<float>(t1 - t0);
+    out[1] = static_cast<float>(t2 - t0);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
 }  // namespace fwa2
+
+extern "C" int fwa2_selftest_mma_timing(int n, int a_tmem, int chains, int count, float* out,
+                                        void* status, void* stream) {
+  using namespace fwa2;
+  if (n < 16 || n > 256 || (n % 16) != 0 || (chains != 1 && chains != 2 && chains != 4 && chains != 8) || count < 1 || count > 4096) return -1;
+  const size_t smem = 65536 + 2048;
+  cudaError_t e = cudaFuncSetAttribute(mma_timing_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return -100 - static_cast<int>(e);
+  mma_timing_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      n, a_tmem, chains, count, out, static_cast<DeviceStatus*>(status));
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
+}
 
 extern "C" int fwa2_selftest_mma(int mode, int dtype, const void* a, const void* b, float* d,
                                  void* status, void* stream) {

@@ -79,7 +79,7 @@ def _stream(device) -> C.c_void_p:
 
 
 def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="scalar",
-                        _variant: int = 0, _max_ctas: int = 0):
+                        _variant: int = 0, _max_ctas: int = 0, _trace=None):
     batch_window_size, n_heads, seqlen_q, d = q.shape
     _, _, seqlen_k, _ = k.shape
     assert k.shape == (batch_window_size, n_heads, seqlen_k, d)
@@ -136,6 +136,9 @@ def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="
     a.status = _status(q.device).data_ptr()
     a.variant = _variant
     a.max_ctas = _max_ctas
+    if _trace is not None:      # int64 tensor of 4 * entries words: timeline of CTA 0
+        a.trace = _trace.data_ptr()
+        a.trace_entries = _trace.numel() // 4
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().fwa2_forward(C.byref(a), _stream(q.device)), "fwa2_forward")
     return o, lse, logit_scale
@@ -143,7 +146,7 @@ def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="
 
 def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, db,
                          bias=None, mask=None, scale_type="scalar", _partial_out=None,
-                         _variant: int = 0, _max_ctas: int = 0):
+                         _variant: int = 0, _max_ctas: int = 0, _workspace=None, _trace=None):
     """Fills dq, dk, dv (and dscale, db when given) in place; returns None.
 
     `_partial_out` (fp32, H*N*N + H elements) is an extension used by the window-sharded
@@ -192,7 +195,11 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
         ws_bytes = L.fwa2_bwd_workspace_bytes(batch_window_size, n_heads, seqlen_q, n_windows,
                                               1 if has_bias else 0, 1 if mask is not None else 0)
         assert ws_bytes > 0
-        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        if _workspace is not None:
+            assert _workspace.numel() * _workspace.element_size() >= ws_bytes
+            workspace = _workspace
+        else:
+            workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
 
         a = _lib.BwdArgs()
         a.struct_size = C.sizeof(_lib.BwdArgs)
@@ -218,6 +225,9 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
         a.status = _status(q.device).data_ptr()
         a.variant = _variant
         a.max_ctas = _max_ctas
+        if _trace is not None:
+            a.trace = _trace.data_ptr()
+            a.trace_entries = _trace.numel() // 4
         _lib.check(L.fwa2_backward(C.byref(a), _stream(q.device)), "fwa2_backward")
 
     for dst, src in zip((dq, dk, dv), outs):

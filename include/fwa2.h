@@ -38,6 +38,12 @@ enum fwa2_error {
   FWA2_ERR_LAUNCH = -11        /* the CUDA runtime refused the launch (see fwa2_last_cuda_error) */
 };
 
+/* Bits of fwa2_fwd_args.variant / fwa2_bwd_args.variant (0 = normal operation). */
+#define FWA2_FWD_P_IN_SMEM 1     /* forward: stage P through shared memory instead of TMEM */
+#define FWA2_BWD_SKIP_TABLES 2   /* backward: the workspace still holds the transposed tables of an
+                                    identical earlier call (used to time the main kernel alone) */
+#define FWA2_BWD_SKIP_REDUCE 4   /* backward: leave the per-CTA partials in the workspace */
+
 /* A (BW, H, N, 32) tensor of 16-bit elements with unit stride along the last axis.
  * Strides are in elements. */
 typedef struct fwa2_tensor4 {
@@ -65,8 +71,13 @@ typedef struct fwa2_fwd_args {
   int64_t bias_row_stride, mask_row_stride;  /* elements; multiples of 8 */
   void* status;             /* optional 16-byte device word block written only on a device-side
                                timeout (must be zero-initialised by the caller); may be NULL */
-  int32_t variant;          /* 0 = default; 1 = keep P in shared memory instead of tensor memory */
+  int32_t variant;          /* FWA2_FWD_* bits */
   int32_t max_ctas;         /* 0 = default (fill the device); otherwise an upper bound on the grid */
+  uint64_t* trace;          /* optional device buffer of 4 * trace_entries words: CTA 0 records a
+                               timeline there, one region per role, each word = (clock64 << 8) | event
+                               id; NULL = no tracing */
+  int32_t trace_entries;
+  int32_t reserved0;
 } fwa2_fwd_args;
 
 /* Arguments of the backward pass.
@@ -96,8 +107,11 @@ typedef struct fwa2_bwd_args {
   void* workspace;          /* at least fwa2_bwd_workspace_bytes() bytes, 256-byte aligned */
   size_t workspace_bytes;
   void* status;
-  int32_t variant;
+  int32_t variant;          /* FWA2_BWD_* bits */
   int32_t max_ctas;
+  uint64_t* trace;          /* as in fwa2_fwd_args */
+  int32_t trace_entries;
+  int32_t reserved0;
 } fwa2_bwd_args;
 
 int fwa2_abi_version(void);
@@ -123,6 +137,11 @@ int fwa2_finalize_grads(const float* partial, int32_t dtype, int32_t heads, int3
 /* Device self-checks of the tensor-core building blocks (used by the test-suite). */
 int fwa2_selftest_mma(int mode, int dtype, const void* a, const void* b, float* d, void* status,
                       void* stream);
+
+/* Device micro-benchmark: cycles to issue, and to complete, `count` back-to-back tcgen05.mma of
+ * shape 128 x n x 16 alternating between `chains` accumulators; out[0] = issue, out[1] = done. */
+int fwa2_selftest_mma_timing(int n, int a_tmem, int chains, int count, float* out, void* status,
+                             void* stream);
 
 #ifdef __cplusplus
 }
