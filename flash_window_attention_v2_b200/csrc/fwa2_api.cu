@@ -125,12 +125,12 @@ int encode_table3(CUtensorMap* m, const void* ptr, int dtype, int planes, int ro
 int check_common(int dtype, int bw, int heads, int n, int head_dim, int n_windows, bool has_mask) {
   if (dtype != FWA2_F16 && dtype != FWA2_BF16) return FWA2_ERR_DTYPE;
   if (head_dim != kHeadDim) return FWA2_ERR_HEAD_DIM;
-  if (bw <= 0 || heads <= 0 || n <= 0 || n > 640) return FWA2_ERR_SHAPE;
+  if (bw <= 0 || heads <= 0 || heads > 192 || n <= 0 || n > 640) return FWA2_ERR_SHAPE;
   if (has_mask && (n_windows <= 0 || (bw % n_windows) != 0)) return FWA2_ERR_SHAPE;
   return FWA2_OK;
 }
 
-constexpr uint32_t kCtrlBytes = 512;
+constexpr uint32_t kCtrlBytes = 1024;   // mbarriers + control words [0, 256), per-head scales [256, 1024)
 
 size_t align256(size_t x) { return (x + 255u) & ~static_cast<size_t>(255u); }
 
@@ -344,7 +344,7 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   p.dv = a->dv.ptr; p.dv_sbw = a->dv.stride_bw; p.dv_sh = a->dv.stride_h; p.dv_sn = a->dv.stride_n;
   p.lse = a->lse; p.lse_sbw = a->lse_stride_bw; p.lse_sh = a->lse_stride_h;
   p.scale = a->logit_scale; p.scale_is_tensor = a->scale_is_tensor;
-  p.db_partial = has_bias ? reinterpret_cast<float*>(ws + pl.off_db) : nullptr;
+  p.db_partial = (has_bias && (a->variant & FWA2_BWD_SKIP_DBIAS) == 0) ? reinterpret_cast<float*>(ws + pl.off_db) : nullptr;
   p.db_pitch = pl.db_pitch;
   p.db_buf_stride = static_cast<long long>(a->n) * pl.db_pitch;
   p.dscale_partial = reinterpret_cast<float*>(ws + pl.off_dscale);
@@ -367,9 +367,12 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
            nkv * static_cast<uint32_t>(p.rows_kv) * 4u + 3u * 1024u + kCtrlBytes;
   };
   const uint32_t budget = static_cast<uint32_t>(dev.max_smem_optin);
-  const uint32_t opts[][3] = {{2, 2, 2}, {2, 1, 2}, {1, 2, 2}, {1, 1, 2}, {1, 1, 1}};
+  // preference order; a job of one tile (at most 128 keys) wants three K/V stages, see
+  // bwd_num_sets() in the kernel
+  const uint32_t opts[][3] = {{3, 2, 2}, {3, 1, 2}, {2, 2, 2}, {2, 1, 2}, {1, 2, 2}, {1, 1, 2}, {1, 1, 1}};
   uint32_t nkv = 0, nds = 0, nbm = 0;
   for (const auto& o : opts) {
+    if (o[0] == 3 && p.rows_kv > 128) continue;
     if (total(o[0], o[1], o[2]) <= budget) { nkv = o[0]; nds = o[1]; nbm = o[2]; break; }
   }
   if (nkv == 0) return FWA2_ERR_SHAPE;

@@ -22,22 +22,38 @@ constexpr int kBwdThreads = 320;
 constexpr uint32_t kBwdTmemCols = 512;
 constexpr uint32_t kTmST = 0;       // S^T of warpgroup w at 128 w (64 columns), P^T written over it
 constexpr uint32_t kTmDPT = 64;     // dP^T of warpgroup w at 128 w + 64, dS^T written over it
-constexpr uint32_t kTmDV = 256;     // 32 columns
-constexpr uint32_t kTmDK = 288;     // 32 columns
-constexpr uint32_t kTmDQ = 320;     // 32 columns per 128-query tile, at most 5 tiles
+// Accumulators.  Windows of at most 256 tokens (two query tiles) get TWO sets, so that the
+// epilogue of one key block / job can run one tile late while the tensor core already fills the
+// other set; larger windows have room for one set only.
+//   two sets:  dV[s] 256 + 64 s, dK[s] 288 + 64 s, dQ[s][i] 384 + 64 s + 32 i   (i < 2)
+//   one set:   dV 256, dK 288, dQ[i] 320 + 32 i                                  (i < 5)
+__device__ __forceinline__ uint32_t tm_dv(uint32_t set) { return 256u + 64u * set; }
+__device__ __forceinline__ uint32_t tm_dk(uint32_t set) { return 288u + 64u * set; }
+__device__ __forceinline__ uint32_t tm_dq(uint32_t nsets, uint32_t set, uint32_t i) {
+  return (nsets == 2u ? 384u + 64u * set : 320u) + 32u * i;
+}
 constexpr uint32_t kQdoStageBytes = 4u * kBoxBytes;   // [Q tile | dO tile]
 constexpr uint32_t kDsTileBytes = 32768u;
 constexpr int kNumQdoStages = 3;
 
 enum BwdBar : int {
-  kbKvFull = 0, kbKvReady = 2, kbKvFree = 4,
-  kbQdoFull = 6, kbQdoReady = 9, kbQdoFree = 12,
-  kbStFull = 15, kbPtFull = 17,
-  kbBmFull = 19, kbBmFree = 23,       // index + 2 * warpgroup + stage
-  kbDsFree = 27,
-  kbDkvFull = 29, kbDkvFree = 30, kbDqFull = 31, kbDqFree = 32,
-  kBwdNumBars = 33
+  kbKvFull = 0, kbKvReady = 3, kbKvFree = 6,          // up to three K/V stages
+  kbQdoFull = 9, kbQdoReady = 12, kbQdoFree = 15,
+  kbStFull = 18, kbPtFull = 20,
+  kbBmFull = 22, kbBmFree = 26,       // index + 2 * warpgroup + stage
+  kbDsFree = 30,
+  kbDkvFull = 32, kbDkvFree = 34, kbDqFull = 36, kbDqFree = 38,   // one per accumulator set
+  kBwdNumBars = 40
 };
+
+// Epilogues may run one tile late (two accumulator sets) when the window has at most two query
+// tiles and the K/V stage a late epilogue still reads cannot be the one the next-but-one job
+// needs: jobs of a single tile need three stages for that, longer jobs two.
+__device__ __forceinline__ uint32_t bwd_num_sets(const BwdParams& p, int kb, int mt) {
+  if (mt > 2) return 1u;
+  if (kb * mt >= 2) return p.n_kv_stages >= 2 ? 2u : 1u;
+  return p.n_kv_stages >= 3 ? 2u : 1u;
+}
 
 struct BwdGeom {
   int N, H, pair, KB, MT, h, slot, nslots, count, njobs;
@@ -234,9 +250,147 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     return true;
   };
 
+  const uint32_t nsets = bwd_num_sets(p, g.KB, g.MT);
+  const uint32_t sets_mask = nsets - 1u, sets_shift = nsets - 1u;
   uint32_t jt = 0, nst = 0, kdkv = 0, kdq = 0;
   Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS), bm_ring(NBM);
   TraceCursor tr = (lt == 0) ? trace_begin(p.trace, wg == 0 ? 0 : 3) : TraceCursor{nullptr, 0};
+  // ---- dK, dV of one key block (thread = key): warpgroup 0 writes dV, warpgroup 1 writes dK ----
+  auto dkv_epilogue = [&](const TileIt& it, uint32_t kvs_e, uint32_t kd) -> bool {
+      // dK, dV of key block it.j are complete
+      const uint32_t set = kd & sets_mask, use = kd >> sets_shift;
+      if (!mbar_wait(bar(kbDkvFull + set), use & 1u, ctx, 55)) return false;
+      tc_fence_after();
+      trace_ev(tr, 10);
+      const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
+      const int bw = bwd_bw(p, g, it.t, m);
+      const int jg = g.pair ? static_cast<int>(lt & 63u) : it.j * kTileRows + static_cast<int>(lt);
+      const bool ok = bw < p.BW && jg < g.N;
+      uint32_t r[32];
+      tmem_ld32(tmem + lane_base + (wg == 0 ? tm_dv(set) : tm_dk(set)), r);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar(kbDkvFree + set));
+      if (wg == 0) {
+        if (ok) {
+          uint16_t* dst = static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + jg * p.dv_sn;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 v;
+            v.x = Elem<T>::pack(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
+            v.y = Elem<T>::pack(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
+            v.z = Elem<T>::pack(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
+            v.w = Elem<T>::pack(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + ch * 8) = v;
+          }
+        }
+      } else {
+        // dk = scale * (dK' - k^ (k^ . dK')) / |k|
+        const uint32_t krow = g.pair ? lt : static_cast<uint32_t>(it.j) * kTileRows + lt;
+        const uint32_t k_base = smem_base + p.off_kv + kvs_e * p.kv_stage_bytes;
+        float kh[32];
+        float dot = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t w[4];
+          lds128(k_base + sw64_offset(krow, ch), w);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            kh[ch * 8 + 2 * i] = Elem<T>::lo(w[i]);
+            kh[ch * 8 + 2 * i + 1] = Elem<T>::hi(w[i]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dot = fmaf(kh[i], __uint_as_float(r[i]), dot);
+        const float f = scale * rk_arr[kvs_e * p.rows_kv + krow];
+        if (ok) {
+          uint16_t* dst = static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + jg * p.dk_sn;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            float o8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              o8[i] = f * (__uint_as_float(r[ch * 8 + i]) - kh[ch * 8 + i] * dot);
+            uint4 v;
+            v.x = Elem<T>::pack(o8[0], o8[1]);
+            v.y = Elem<T>::pack(o8[2], o8[3]);
+            v.z = Elem<T>::pack(o8[4], o8[5]);
+            v.w = Elem<T>::pack(o8[6], o8[7]);
+            *reinterpret_cast<uint4*>(dst + ch * 8) = v;
+          }
+        }
+      }
+      if (it.j == g.KB - 1) mbar_arrive(bar(kbKvFree + kvs_e));   // K^ in shared memory no longer needed
+      trace_ev(tr, 11);
+
+    return true;
+  };
+  // ---- dQ of a job (thread = query): warpgroup (i mod 2) writes query tile i ----
+  auto dq_epilogue = [&](int t_e, uint32_t kq) -> bool {
+        // dQ of every query tile of the job is complete
+        const uint32_t set = kq & sets_mask, use = kq >> sets_shift;
+        if (!mbar_wait(bar(kbDqFull + set), use & 1u, ctx, 56)) return false;
+        tc_fence_after();
+        trace_ev(tr, 12);
+        for (int i = static_cast<int>(wg); i < g.MT; i += 2) {
+          const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
+          const int bwq = bwd_bw(p, g, t_e, mq);
+          const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
+          const bool okq = bwq < p.BW && ig < g.N;
+          uint32_t rq[32];
+          tmem_ld32(tmem + lane_base + tm_dq(nsets, set, static_cast<uint32_t>(i)), rq);
+          tmem_wait_ld();
+          if (okq) {
+            const uint16_t* qrow = static_cast<const uint16_t*>(p.q) + bwq * p.q_sbw + g.h * p.q_sh + ig * p.q_sn;
+            float qv[32];
+            float ss = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              const uint4 v = ldg_nc_v4(qrow + ch * 8);
+              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                qv[ch * 8 + 2 * e] = Elem<T>::lo(w[e]);
+                qv[ch * 8 + 2 * e + 1] = Elem<T>::hi(w[e]);
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ss = fmaf(qv[e], qv[e], ss);
+            const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+            float dot = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              qv[e] *= rn;
+              dot = fmaf(qv[e], __uint_as_float(rq[e]), dot);
+            }
+            dscale_acc += dot;
+            const float f = scale * rn;
+            uint16_t* dst = static_cast<uint16_t*>(p.dq) + bwq * p.dq_sbw + g.h * p.dq_sh + ig * p.dq_sn;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              float o8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                o8[e] = f * (__uint_as_float(rq[ch * 8 + e]) - qv[ch * 8 + e] * dot);
+              uint4 v;
+              v.x = Elem<T>::pack(o8[0], o8[1]);
+              v.y = Elem<T>::pack(o8[2], o8[3]);
+              v.z = Elem<T>::pack(o8[4], o8[5]);
+              v.w = Elem<T>::pack(o8[6], o8[7]);
+              *reinterpret_cast<uint4*>(dst + ch * 8) = v;
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar(kbDqFree + set));
+        trace_ev(tr, 13);
+    return true;
+  };
+  bool pend_dkv = false, pend_dq = false;
+  TileIt pd_it{0, 0, 0};
+  uint32_t pd_kvs = 0, pd_k = 0, pq_k = 0;
+  int pq_t = 0;
+
   TileIt cur{0, 0, 0};
   uint4 o_row[4] = {};
   float lse_pf = 0.f;
@@ -299,7 +453,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       const float* delta = rowstats + qs * 256u + 128u + wg * 64u;
       const long long db_buf = g.pair ? 2ll * blockIdx.x + wg : static_cast<long long>(blockIdx.x);
       const int ig0 = g.pair ? 0 : cur.i * kTileRows + static_cast<int>(wg) * kStepCols;
-      float* db_row = (p.has_bias && key_ok)
+      float* db_row = (p.db_partial != nullptr && key_ok)
                           ? p.db_partial + db_buf * p.db_buf_stride + static_cast<long long>(jg) * p.db_pitch + ig0
                           : nullptr;
       const bool db_store = (jt == 0);
@@ -360,135 +514,42 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     }
 
     // ------------------------------ epilogues ------------------------------
+    // With two accumulator sets they run one tile late: by then the products they read have
+    // long been finished, and the tensor core is not left waiting for this warpgroup either.
+    if (pend_dkv) {
+      if (!dkv_epilogue(pd_it, pd_kvs, pd_k)) return;
+      pend_dkv = false;
+    }
+    if (pend_dq) {
+      if (!dq_epilogue(pq_t, pq_k)) return;
+      pend_dq = false;
+    }
     if (cur.i == g.MT - 1) {
-      // dK, dV of key block cur.j are complete
-      if (!mbar_wait(bar(kbDkvFull), kdkv & 1u, ctx, 55)) return;
-      ++kdkv;
-      tc_fence_after();
-      trace_ev(tr, 10);
-      const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
-      const int bw = bwd_bw(p, g, cur.t, m);
-      const int jg = g.pair ? static_cast<int>(lt & 63u) : cur.j * kTileRows + static_cast<int>(lt);
-      const bool ok = bw < p.BW && jg < g.N;
-      uint32_t r[32];
-      tmem_ld32(tmem + lane_base + (wg == 0 ? kTmDV : kTmDK), r);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar(kbDkvFree));
-      if (wg == 0) {
-        if (ok) {
-          uint16_t* dst = static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + jg * p.dv_sn;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint4 v;
-            v.x = Elem<T>::pack(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
-            v.y = Elem<T>::pack(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
-            v.z = Elem<T>::pack(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
-            v.w = Elem<T>::pack(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
-            *reinterpret_cast<uint4*>(dst + ch * 8) = v;
-          }
-        }
+      if (nsets == 2u) {
+        pend_dkv = true; pd_it = cur; pd_kvs = kvs; pd_k = kdkv;
       } else {
-        // dk = scale * (dK' - k^ (k^ . dK')) / |k|
-        const uint32_t krow = g.pair ? lt : static_cast<uint32_t>(cur.j) * kTileRows + lt;
-        const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
-        float kh[32];
-        float dot = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t w[4];
-          lds128(k_base + sw64_offset(krow, ch), w);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            kh[ch * 8 + 2 * i] = Elem<T>::lo(w[i]);
-            kh[ch * 8 + 2 * i + 1] = Elem<T>::hi(w[i]);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) dot = fmaf(kh[i], __uint_as_float(r[i]), dot);
-        const float f = scale * rk_arr[kvs * p.rows_kv + krow];
-        if (ok) {
-          uint16_t* dst = static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + jg * p.dk_sn;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            float o8[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              o8[i] = f * (__uint_as_float(r[ch * 8 + i]) - kh[ch * 8 + i] * dot);
-            uint4 v;
-            v.x = Elem<T>::pack(o8[0], o8[1]);
-            v.y = Elem<T>::pack(o8[2], o8[3]);
-            v.z = Elem<T>::pack(o8[4], o8[5]);
-            v.w = Elem<T>::pack(o8[6], o8[7]);
-            *reinterpret_cast<uint4*>(dst + ch * 8) = v;
-          }
-        }
+        if (!dkv_epilogue(cur, kvs, kdkv)) return;
       }
-      if (cur.j == g.KB - 1) mbar_arrive(bar(kbKvFree + kvs));   // K^ in shared memory no longer needed
-      trace_ev(tr, 11);
-
+      ++kdkv;
       if (cur.j == g.KB - 1) {
-        // dQ of every query tile of the job is complete
-        if (!mbar_wait(bar(kbDqFull), kdq & 1u, ctx, 56)) return;
-        ++kdq;
-        tc_fence_after();
-        trace_ev(tr, 12);
-        for (int i = static_cast<int>(wg); i < g.MT; i += 2) {
-          const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
-          const int bwq = bwd_bw(p, g, cur.t, mq);
-          const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
-          const bool okq = bwq < p.BW && ig < g.N;
-          uint32_t rq[32];
-          tmem_ld32(tmem + lane_base + kTmDQ + 32u * i, rq);
-          tmem_wait_ld();
-          if (okq) {
-            const uint16_t* qrow = static_cast<const uint16_t*>(p.q) + bwq * p.q_sbw + g.h * p.q_sh + ig * p.q_sn;
-            float qv[32];
-            float ss = 0.f;
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-              const uint4 v = ldg_nc_v4(qrow + ch * 8);
-              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                qv[ch * 8 + 2 * e] = Elem<T>::lo(w[e]);
-                qv[ch * 8 + 2 * e + 1] = Elem<T>::hi(w[e]);
-              }
-            }
-#pragma unroll
-            for (int e = 0; e < 32; ++e) ss = fmaf(qv[e], qv[e], ss);
-            const float rn = rsqrtf(fmaxf(ss, 1e-24f));
-            float dot = 0.f;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              qv[e] *= rn;
-              dot = fmaf(qv[e], __uint_as_float(rq[e]), dot);
-            }
-            dscale_acc += dot;
-            const float f = scale * rn;
-            uint16_t* dst = static_cast<uint16_t*>(p.dq) + bwq * p.dq_sbw + g.h * p.dq_sh + ig * p.dq_sn;
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-              float o8[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                o8[e] = f * (__uint_as_float(rq[ch * 8 + e]) - qv[ch * 8 + e] * dot);
-              uint4 v;
-              v.x = Elem<T>::pack(o8[0], o8[1]);
-              v.y = Elem<T>::pack(o8[2], o8[3]);
-              v.z = Elem<T>::pack(o8[4], o8[5]);
-              v.w = Elem<T>::pack(o8[6], o8[7]);
-              *reinterpret_cast<uint4*>(dst + ch * 8) = v;
-            }
-          }
+        if (nsets == 2u) {
+          pend_dq = true; pq_t = cur.t; pq_k = kdq;
+        } else {
+          if (!dq_epilogue(cur.t, kdq)) return;
         }
-        tc_fence_before();
-        mbar_arrive(bar(kbDqFree));
-        trace_ev(tr, 13);
+        ++kdq;
       }
     }
 
-    if (!has_next) break;
+    if (!has_next) {
+      if (pend_dkv) {
+        if (!dkv_epilogue(pd_it, pd_kvs, pd_k)) return;
+      }
+      if (pend_dq) {
+        if (!dq_epilogue(pq_t, pq_k)) return;
+      }
+      break;
+    }
     if (defer_job) {
       if (!prologue_job(kv_next)) return;
     }
@@ -549,6 +610,8 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
   };
 
   uint32_t kdkv = 0, kdq = 0;
+  const uint32_t nsets = bwd_num_sets(p, g.KB, g.MT);
+  const uint32_t sets_mask = nsets - 1u, sets_shift = nsets - 1u;
   TraceCursor tr = trace_begin(p.trace, 1);
   uint32_t nst[2] = {0u, 0u};
   Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS);
@@ -577,9 +640,9 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
 
     if (cur.i == 0) {
       // the previous key block's dK / dV must have been read out before they are overwritten
-      if (!mbar_wait(bar(kbDkvFree), (kdkv & 1u) ^ 1u, ctx, 62)) return;
+      if (!mbar_wait(bar(kbDkvFree + (kdkv & sets_mask)), ((kdkv >> sets_shift) & 1u) ^ 1u, ctx, 62)) return;
       if (cur.j == 0) {
-        if (!mbar_wait(bar(kbDqFree), (kdq & 1u) ^ 1u, ctx, 63)) return;
+        if (!mbar_wait(bar(kbDqFree + (kdq & sets_mask)), ((kdq >> sets_shift) & 1u) ^ 1u, ctx, 63)) return;
       }
     }
     for (int w = 0; w < 2; ++w) {
@@ -593,8 +656,10 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
         const uint32_t a_p = tmem + w * 128u + kTmST, a_ds = tmem + w * 128u + kTmDPT;
 #pragma unroll
         for (uint32_t k = 0; k < 4; ++k) {
-          mma_ts(tmem + kTmDV, a_p + k * 8u, desc_at(dm64, b.dO + row_off + k * 1024u), idesc_acc, first | k);
-          mma_ts(tmem + kTmDK, a_ds + k * 8u, desc_at(dm64, b.q + row_off + k * 1024u), idesc_acc, first | k);
+          mma_ts(tmem + tm_dv(kdkv & sets_mask), a_p + k * 8u, desc_at(dm64, b.dO + row_off + k * 1024u),
+                 idesc_acc, first | k);
+          mma_ts(tmem + tm_dk(kdkv & sets_mask), a_ds + k * 8u, desc_at(dm64, b.q + row_off + k * 1024u),
+                 idesc_acc, first | k);
         }
       }
       trace_ev(tr, 32 + w);
@@ -614,7 +679,7 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
     {
       const uint32_t ds_base = smem_base + p.off_ds + ds_ring.stage * kDsTileBytes;
       const uint32_t kb = b.k + (g.pair ? 0u : static_cast<uint32_t>(cur.j) * (kTileRows * kRowBytes));
-      const uint32_t dq_col = tmem + kTmDQ + 32u * cur.i;
+      const uint32_t dq_col = tmem + tm_dq(nsets, kdq & sets_mask, static_cast<uint32_t>(cur.i));
       const uint32_t first = cur.j > 0 ? 1u : 0u;
 #pragma unroll
       for (uint32_t k = 0; k < 8; ++k)
@@ -624,10 +689,10 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
     mma_commit(bar(kbQdoFree + qdo_ring.stage));
     trace_ev(tr, 36);
     if (cur.i == g.MT - 1) {
-      mma_commit(bar(kbDkvFull));
+      mma_commit(bar(kbDkvFull + (kdkv & sets_mask)));
       ++kdkv;
       if (cur.j == g.KB - 1) {
-        mma_commit(bar(kbDqFull));
+        mma_commit(bar(kbDqFull + (kdq & sets_mask)));
         ++kdq;
         mma_commit(bar(kbKvFree + kv_ring.stage));
       }
@@ -821,7 +886,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
       else if (i >= kbQdoReady && i < kbQdoFree) count = 256u;
       else if (i >= kbPtFull && i < kbBmFull) count = 128u;
       else if (i >= kbBmFree && i < kbDsFree) count = 128u;
-      else if (i == kbDkvFree || i == kbDqFree) count = 256u;
+      else if ((i >= kbDkvFree && i < kbDqFull) || (i >= kbDqFree && i < kBwdNumBars)) count = 256u;
       mbar_init(bars + 8u * i, count);
     }
     mbar_fence_init();

@@ -47,7 +47,7 @@ __device__ __forceinline__ FwdShape fwd_shape(const FwdParams& p) {
 // ------------------------------------------------------------------------------------------------
 template <typename T, bool kPTmem>
 __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_t bars,
-                                 uint32_t tmem, const WaitCtx& ctx) {
+                                 uint32_t tmem, const WaitCtx& ctx, const float* scale_tab) {
   const FwdShape sh = fwd_shape(p);
   const uint32_t tid = threadIdx.x;          // 0..127 = row of the tile
   const uint32_t hf = tid >> 6;
@@ -75,33 +75,51 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
   uint32_t tt = 0, pvc = 0;
   Ring kv_ring(p.n_kv_stages), s_ring(sh.pair ? 1u : 2u), bm_ring(p.n_bm_stages);
   TraceCursor tr = (tid == 0) ? trace_begin(p.trace, 0) : TraceCursor{nullptr, 0};
-  for (int job = blockIdx.x; job < p.n_jobs; job += gridDim.x, kv_ring.advance()) {
-    const int unit = sh.pair ? 2 * job + static_cast<int>(hf) : job;
-    const bool unit_ok = unit < sh.U;
-    const int bw = unit / sh.H, h = unit - bw * sh.H;
-    const float scale = load_scale<T>(p.scale, p.scale_is_tensor, h);
-
-    // ---- normalise the K rows of this job in place ----
-    const uint32_t kvs = kv_ring.stage;
+  // ---- K rows of a job: normalised in place ----
+  auto prologue_kv = [&](const Ring& r) -> bool {
+    const uint32_t kvs = r.stage;
     const uint32_t kv_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
-    if (!mbar_wait(bar(kBarKvFull + kvs), kv_ring.phase, ctx, 10)) return;
+    if (!mbar_wait(bar(kBarKvFull + kvs), r.phase, ctx, 10)) return false;
     trace_ev(tr, 1);
     for (uint32_t rr = tid; rr < static_cast<uint32_t>(sh.rows_kv); rr += 128u)
       normalise_row<T>(kv_base, rr);
     fence_proxy_async_smem();
     mbar_arrive(bar(kBarKvReady + kvs));
     trace_ev(tr, 2);
+    return true;
+  };
+  // ---- my Q row of a tile: normalised in place ----
+  auto prologue_q = [&](uint32_t ttn) -> bool {
+    const uint32_t qs = ttn & 1u;
+    const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
+    if (!mbar_wait(bar(kBarQFull + qs), (ttn >> 1) & 1u, ctx, 11)) return false;
+    trace_ev(tr, 3);
+    normalise_row<T>(q_base, tid);
+    fence_proxy_async_smem();
+    mbar_arrive(bar(kBarQReady + qs));
+    trace_ev(tr, 4);
+    return true;
+  };
+  // The prologue of the NEXT tile runs before the epilogue of the current one, so that the MMA
+  // warp can already produce the next scores while this tile's output is written.
+  bool kv_ahead = false, q_ahead = false;
+
+  for (int job = blockIdx.x; job < p.n_jobs; job += gridDim.x, kv_ring.advance()) {
+    const int unit = sh.pair ? 2 * job + static_cast<int>(hf) : job;
+    const bool unit_ok = unit < sh.U;
+    const int bw = unit / sh.H, h = unit - bw * sh.H;
+    const float scale = scale_tab[h];
+
+    if (!kv_ahead) {
+      if (!prologue_kv(kv_ring)) return;
+    }
+    kv_ahead = false;
 
     for (int mt = 0; mt < sh.MT; ++mt, ++tt) {
-      // ---- normalise my Q row ----
-      const uint32_t qs = tt & 1u;
-      const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
-      if (!mbar_wait(bar(kBarQFull + qs), (tt >> 1) & 1u, ctx, 11)) return;
-      trace_ev(tr, 3);
-      normalise_row<T>(q_base, tid);
-      fence_proxy_async_smem();
-      mbar_arrive(bar(kBarQReady + qs));
-      trace_ev(tr, 4);
+      if (!q_ahead) {
+        if (!prologue_q(tt)) return;
+      }
+      q_ahead = false;
 
       const int row = sh.pair ? static_cast<int>(tid & 63u) : mt * kTileRows + static_cast<int>(tid);
       const bool row_ok = unit_ok && row < sh.N;
@@ -240,6 +258,19 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
         }
         mbar_arrive(bar(kBarPFull));
         trace_ev(tr, 15);
+      }
+
+      // ---- prologue of the next tile (and job) ----
+      if (mt + 1 < sh.MT) {
+        if (!prologue_q(tt + 1)) return;
+        q_ahead = true;
+      } else if (job + static_cast<int>(gridDim.x) < p.n_jobs && p.n_kv_stages >= 2) {
+        Ring nx = kv_ring;
+        nx.advance();
+        if (!prologue_kv(nx)) return;
+        kv_ahead = true;
+        if (!prologue_q(tt + 1)) return;
+        q_ahead = true;
       }
 
       // ---- last P*V of the tile, then the epilogue ----
@@ -533,6 +564,10 @@ __global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_consta
     tmem_alloc(smem_u32(&tmem_slot), kFwdTmemCols);
     tmem_relinquish();
   }
+  // per-head score multipliers, looked up from shared memory in the per-job path
+  float* scale_tab = reinterpret_cast<float*>(smem_raw + p.off_ctrl + 256u);
+  for (int hh = static_cast<int>(tid); hh < p.H; hh += kFwdThreads)
+    scale_tab[hh] = load_scale<T>(p.scale, p.scale_is_tensor, hh);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -540,7 +575,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_consta
   WaitCtx ctx{&ctrl_words[1], p.status};
 
   if (warp < 4) {
-    fwd_softmax_role<T, kPTmem>(p, smem_base, bars, tmem, ctx);
+    fwd_softmax_role<T, kPTmem>(p, smem_base, bars, tmem, ctx, scale_tab);
   } else if (lane == 0) {
     if (warp == 4) fwd_mma_role<T, kPTmem>(p, smem_base, bars, tmem, ctx);
     else fwd_load_role(p, smem_base, bars, ctx);

@@ -28,7 +28,7 @@ enum fwa2_error {
   FWA2_ERR_NULL = -1,          /* a required pointer is null */
   FWA2_ERR_DTYPE = -2,         /* dtype is not f16 / bf16 */
   FWA2_ERR_HEAD_DIM = -3,      /* head dimension other than 32 */
-  FWA2_ERR_SHAPE = -4,         /* non-positive size, N > 640, BW not a multiple of nW, ... */
+  FWA2_ERR_SHAPE = -4,         /* non-positive size, N > 640, heads > 192, BW not a multiple of nW */
   FWA2_ERR_STRIDE = -5,        /* a stride that TMA cannot express (not a multiple of 8 elements) */
   FWA2_ERR_ALIGN = -6,         /* a base pointer that is not 16-byte aligned */
   FWA2_ERR_WORKSPACE = -7,     /* workspace missing or too small */
@@ -43,6 +43,8 @@ enum fwa2_error {
 #define FWA2_BWD_SKIP_TABLES 2   /* backward: the workspace still holds the transposed tables of an
                                     identical earlier call (used to time the main kernel alone) */
 #define FWA2_BWD_SKIP_REDUCE 4   /* backward: leave the per-CTA partials in the workspace */
+#define FWA2_BWD_SKIP_DBIAS 8    /* backward, timing experiments only: do not accumulate dBias
+                                    (dbias then holds garbage) */
 
 /* A (BW, H, N, 32) tensor of 16-bit elements with unit stride along the last axis.
  * Strides are in elements. */
