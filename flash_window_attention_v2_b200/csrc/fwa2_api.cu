@@ -187,6 +187,7 @@ extern "C" const char* fwa2_strerror(int code) {
     case FWA2_ERR_TENSOR_MAP: return "tensor map encoding failed";
     case FWA2_ERR_ABI: return "struct_size / abi_version mismatch";
     case FWA2_ERR_LAUNCH: return "kernel launch failed";
+    case FWA2_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the built-in static array holds";
     default: return "unknown error";
   }
 }

@@ -35,7 +35,9 @@ enum fwa2_error {
   FWA2_ERR_DRIVER = -8,        /* the CUDA driver entry point for tensor maps is unavailable */
   FWA2_ERR_TENSOR_MAP = -9,    /* cuTensorMapEncodeTiled rejected a descriptor */
   FWA2_ERR_ABI = -10,          /* struct_size / abi_version mismatch */
-  FWA2_ERR_LAUNCH = -11        /* the CUDA runtime refused the launch (see fwa2_last_cuda_error) */
+  FWA2_ERR_LAUNCH = -11,       /* the CUDA runtime refused the launch (see fwa2_last_cuda_error) */
+  FWA2_ERR_SCRATCH_LIMIT = -12 /* fwa2_backward_static_scratch: the problem needs more scratch than
+                                  FWA2_STATIC_SCRATCH_BYTES */
 };
 
 /* Bits of fwa2_fwd_args.variant / fwa2_bwd_args.variant (0 = normal operation). */
@@ -135,6 +137,27 @@ int fwa2_backward(const fwa2_bwd_args* args, void* stream);
  * (attn_kernel_backward.py:703-711).  dbias / dscale may be NULL. */
 int fwa2_finalize_grads(const float* partial, int32_t dtype, int32_t heads, int32_t n,
                         const void* logit_scale, void* dbias, void* dscale, void* stream);
+
+/* Backward pass that allocates nothing and takes no workspace.  (No counterpart in the reference
+ * project, which allocates its fp32 accumulators with torch on every call.)
+ *
+ * For callers that cannot provide scratch memory: code between cudaStreamBeginCapture and
+ * cudaStreamEndCapture, where cudaMalloc is not allowed; a plugin inside a framework that keeps
+ * the device allocator to itself; a serving loop that bans allocator calls once it is warm.
+ * Same arguments and results as fwa2_backward, except that `workspace` / `workspace_bytes` are
+ * ignored: the scratch is a fixed array of FWA2_STATIC_SCRATCH_BYTES inside the library's
+ * device image, present on every GPU that loads the library until the process exits.
+ *
+ *  - Problems whose fwa2_bwd_workspace_bytes() exceeds FWA2_STATIC_SCRATCH_BYTES are refused
+ *    with FWA2_ERR_SCRATCH_LIMIT and nothing is launched.
+ *  - The first call on each device looks up the array's device address (the device must be
+ *    current); make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Nothing in it has to be cleared between calls,
+ *    but two calls that can overlap on the GPU (different streams, no dependency) race on it:
+ *    keep them on one stream or order them with events.
+ *  - No cudaMalloc / cudaFree or any other allocating routine is called. */
+#define FWA2_STATIC_SCRATCH_BYTES (48u << 20)
+int fwa2_backward_static_scratch(const fwa2_bwd_args* args, void* stream);
 
 /* Device self-checks of the tensor-core building blocks (used by the test-suite). */
 int fwa2_selftest_mma(int mode, int dtype, const void* a, const void* b, float* d, void* status,
