@@ -72,39 +72,54 @@ __device__ __forceinline__ int units_of(const ReduceParams& p, int s, int w) {
   return w == 0 ? (count + 1) / 2 : count / 2;
 }
 
+// One block sums an 8 (key) x 32 (query) patch of every partial buffer of its head.  The buffer list
+// is dealt round-robin to eight thread rows (threadIdx.y), each of which adds its buffers in
+// ascending order; the eight sub-sums are then added in ascending order as well, so the result
+// does not depend on timing.
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_partials_kernel(const ReduceParams p) {
-  __shared__ float tile[32][33];
+  __shared__ float part[8][8][33];   // [buffer lane][key][query]
   const int h = blockIdx.z;
-  const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
+  const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 8;
   const int tx = threadIdx.x, ty = threadIdx.y;
   if (p.db_partial != nullptr) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const int nw = p.pair ? 2 : 1;
-    for (int s = 0; s < p.nslots; ++s) {
-      for (int w = 0; w < nw; ++w) {
-        if (units_of(p, s, w) == 0) continue;
-        const long long buf = static_cast<long long>(s * p.H + h) * nw + w;
-        const float* src = p.db_partial + buf * p.buf_stride;
+    float acc[8];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const int j = j0 + ty + 8 * r, i = i0 + tx;
-          if (j < p.N && i < p.N) acc[r] += src[static_cast<long long>(j) * p.pitch + i];
+    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+    const int nw = p.pair ? 2 : 1;
+    const int nbuf = p.nslots * nw;
+    const int i = i0 + tx;
+    for (int b = ty; b < nbuf; b += 8) {
+      const int s = b / nw, w = b - s * nw;
+      if (units_of(p, s, w) == 0) continue;
+      const long long buf = static_cast<long long>(s * p.H + h) * nw + w;
+      const float* src = p.db_partial + buf * p.buf_stride;
+      if (i < p.N) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const int j = j0 + r;
+          if (j < p.N) acc[r] += src[static_cast<long long>(j) * p.pitch + i];
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < 4; ++r) tile[ty + 8 * r][tx] = acc[r];   // tile[j][i]
+    for (int r = 0; r < 8; ++r) part[ty][r][tx] = acc[r];
     __syncthreads();
+    // thread (tx, ty) finishes key j0 + ty, query i0 + tx
+    float v = 0.f;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int i = i0 + ty + 8 * r, j = j0 + tx;
-      if (i < p.N && j < p.N) {
-        const float v = tile[tx][ty + 8 * r];
-        const long long idx = (static_cast<long long>(h) * p.N + i) * p.N + j;
-        if (p.out_f32 != nullptr) p.out_f32[idx] = v;
-        else if (p.dbias != nullptr) static_cast<uint16_t*>(p.dbias)[idx] = to_raw16<T>(v);
-      }
+    for (int l = 0; l < 8; ++l) v += part[l][ty][tx];
+    __syncthreads();
+    part[0][ty][tx] = v;
+    __syncthreads();
+    // write transposed: out[h][query][key], eight consecutive keys per query
+    const int q = ty * 4 + (tx >> 3), kk = tx & 7;   // 32 queries x 8 keys
+    const int qi = i0 + q, kj = j0 + kk;
+    if (qi < p.N && kj < p.N) {
+      const float o = part[0][kk][q];
+      const long long idx = (static_cast<long long>(h) * p.N + qi) * p.N + kj;
+      if (p.out_f32 != nullptr) p.out_f32[idx] = o;
+      else if (p.dbias != nullptr) static_cast<uint16_t*>(p.dbias)[idx] = to_raw16<T>(o);
     }
   }
   if (blockIdx.x == 0 && blockIdx.y == 0 && tx == 0 && ty == 0 && p.dscale_partial != nullptr) {
@@ -149,7 +164,7 @@ cudaError_t launch_reduce_partials(const ReduceParams& p, int dtype_is_bf16, cud
   dim3 grid(1, 1, p.H), block(32, 8);
   if (p.db_partial != nullptr) {
     grid.x = (p.N + 31) / 32;
-    grid.y = (p.N + 31) / 32;
+    grid.y = (p.N + 7) / 8;
   }
   if (dtype_is_bf16) reduce_partials_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(p);
   else reduce_partials_kernel<__half><<<grid, block, 0, stream>>>(p);
