@@ -370,10 +370,14 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   const uint32_t budget = static_cast<uint32_t>(dev.max_smem_optin);
   // preference order; a job of one tile (at most 128 keys) wants three K/V stages, see
   // bwd_num_sets() in the kernel
-  const uint32_t opts[][3] = {{3, 2, 2}, {3, 1, 2}, {2, 2, 2}, {2, 1, 2}, {1, 2, 2}, {1, 1, 2}, {1, 1, 1}};
+  // Jobs of a single tile (windows of at most 128 tokens) release their K/V stage only in the
+  // epilogue that runs one tile late, so they want four stages to keep a whole tile of lead for
+  // the next load.
+  const uint32_t opts[][3] = {{4, 2, 2}, {4, 1, 2}, {3, 2, 2}, {3, 1, 2}, {2, 2, 2}, {2, 1, 2},
+                              {1, 2, 2}, {1, 1, 2}, {1, 1, 1}};
   uint32_t nkv = 0, nds = 0, nbm = 0;
   for (const auto& o : opts) {
-    if (o[0] == 3 && p.rows_kv > 128) continue;
+    if (o[0] >= 3 && p.rows_kv > 128) continue;
     if (total(o[0], o[1], o[2]) <= budget) { nkv = o[0]; nds = o[1]; nbm = o[2]; break; }
   }
   if (nkv == 0) return FWA2_ERR_SHAPE;

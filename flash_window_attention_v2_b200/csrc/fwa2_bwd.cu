@@ -11,14 +11,15 @@
 //   warps 0-3   warpgroup 0: thread t owns key t of the tile, queries [0, 64)
 //   warps 4-7   warpgroup 1: same keys, queries [64, 128)
 //   warp  8     issues every tcgen05.mma (one thread)
-//   warp  9     TMA producer (one thread)
+//   warp  9     TMA producer of K/V and Q/dO (one thread)
+//   warps 10-11 TMA producers of the bias / mask tables of warpgroup 0 / 1 (one thread each)
 // Replaces flash_win_attn_v2/kernels/attn_kernel_backward.py:6-51 (delta pre-pass) and
 // :84-564 (`_bwd_kernel`).
 #include "fwa2_common.cuh"
 
 namespace fwa2 {
 
-constexpr int kBwdThreads = 320;
+constexpr int kBwdThreads = 384;
 constexpr uint32_t kBwdTmemCols = 512;
 constexpr uint32_t kTmST = 0;       // S^T of warpgroup w at 128 w (64 columns), P^T written over it
 constexpr uint32_t kTmDPT = 64;     // dP^T of warpgroup w at 128 w + 64, dS^T written over it
@@ -37,13 +38,13 @@ constexpr uint32_t kDsTileBytes = 32768u;
 constexpr int kNumQdoStages = 3;
 
 enum BwdBar : int {
-  kbKvFull = 0, kbKvReady = 3, kbKvFree = 6,          // up to three K/V stages
-  kbQdoFull = 9, kbQdoReady = 12, kbQdoFree = 15,
-  kbStFull = 18, kbPtFull = 20,
-  kbBmFull = 22, kbBmFree = 26,       // index + 2 * warpgroup + stage
-  kbDsFree = 30,
-  kbDkvFull = 32, kbDkvFree = 34, kbDqFull = 36, kbDqFree = 38,   // one per accumulator set
-  kBwdNumBars = 40
+  kbKvFull = 0, kbKvReady = 4, kbKvFree = 8,          // up to four K/V stages
+  kbQdoFull = 12, kbQdoReady = 15, kbQdoFree = 18,
+  kbStFull = 21, kbPtFull = 25,       // index + 2 * warpgroup + chunk
+  kbBmFull = 29, kbBmFree = 33,       // index + 2 * warpgroup + stage
+  kbDsFree = 37,
+  kbDkvFull = 39, kbDkvFree = 41, kbDqFull = 43, kbDqFree = 45,   // one per accumulator set
+  kBwdNumBars = 47
 };
 
 // Epilogues may run one tile late (two accumulator sets) when the window has at most two query
@@ -112,57 +113,53 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* ptr) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// One 32-query chunk of a step for one key (= one thread):
+// Eight queries of a chunk for one key (= one thread):
 //   p = exp2(x log2e - lse2),  ds = p (dP - delta),  x = scale * cos + bias + mask.
-// Produces the packed P^T / dS^T words and adds ds into this CTA's dBias^T partial.
+// Produces the packed P^T / dS^T words and adds ds into this CTA's dBias^T partial.  Queries past
+// the end of the window need no special case: their Q and dO rows were zero-filled by the TMA
+// load and their lse2 is +inf, so p = 0 and ds = 0 exactly.
+//
+// The per-element work is written for eight queries and run in a rolled loop (not unrolled over
+// the 32 queries of a chunk): these kernels are bound by instruction fetch, and the loop body has
+// to stay resident in the instruction cache next to the other roles' code.
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool kRagged>
-__device__ __forceinline__ void bwd_chunk(bool has_bias, bool has_mask, const uint32_t (&sv)[32],
-                                          const uint32_t (&dpv)[32], uint32_t bias_tile,
-                                          uint32_t mask_tile, uint32_t lt, const float* lse2,
-                                          const float* delta, float scale, int rows_left,
-                                          float* db_ptr, bool db_store, uint32_t (&pw)[16],
-                                          uint32_t (&dw)[16]) {
+template <typename T>
+__device__ __forceinline__ void bwd_group(bool has_bias, bool has_mask, const uint32_t (&sv)[8],
+                                          const uint32_t (&dpv)[8], uint32_t bias_addr,
+                                          uint32_t mask_addr, const float* lse2, const float* delta,
+                                          float scale, bool key_ok, float* db_ptr, bool db_store,
+                                          uint32_t (&pw)[4], uint32_t (&dw)[4]) {
+  uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
+  if (has_bias) lds128(bias_addr, wb);
+  if (has_mask) lds128(mask_addr, wm);
+  const float4 la = *reinterpret_cast<const float4*>(lse2);
+  const float4 lb = *reinterpret_cast<const float4*>(lse2 + 4);
+  const float4 da = *reinterpret_cast<const float4*>(delta);
+  const float4 db = *reinterpret_cast<const float4*>(delta + 4);
+  const float l8[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+  const float d8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+  float dsv[8];
 #pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
-    uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
-    if (has_bias) lds128(bias_tile + sw64_offset(lt, ch), wb);
-    if (has_mask) lds128(mask_tile + sw64_offset(lt, ch), wm);
-    const float4 la = *reinterpret_cast<const float4*>(lse2 + ch * 8);
-    const float4 lb = *reinterpret_cast<const float4*>(lse2 + ch * 8 + 4);
-    const float4 da = *reinterpret_cast<const float4*>(delta + ch * 8);
-    const float4 db = *reinterpret_cast<const float4*>(delta + ch * 8 + 4);
-    const float l8[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-    const float d8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-    float dsv[8];
-#pragma unroll
-    for (int e2 = 0; e2 < 4; ++e2) {
-      const int e = 2 * e2, idx = ch * 8 + e;
-      const float x0 = fmaf(__uint_as_float(sv[idx]), scale, Elem<T>::lo(wb[e2])) + Elem<T>::lo(wm[e2]);
-      const float x1 = fmaf(__uint_as_float(sv[idx + 1]), scale, Elem<T>::hi(wb[e2])) + Elem<T>::hi(wm[e2]);
-      float p0 = ex2f(fmaf(x0, kLog2e, -l8[e]));
-      float p1 = ex2f(fmaf(x1, kLog2e, -l8[e + 1]));
-      float s0 = p0 * (__uint_as_float(dpv[idx]) - d8[e]);
-      float s1 = p1 * (__uint_as_float(dpv[idx + 1]) - d8[e + 1]);
-      if (kRagged) {
-        // queries past the end of the window: the accumulator columns were never written
-        if (idx >= rows_left) { p0 = 0.f; s0 = 0.f; }
-        if (idx + 1 >= rows_left) { p1 = 0.f; s1 = 0.f; }
-      }
-      pw[ch * 4 + e2] = Elem<T>::pack(p0, p1);
-      dw[ch * 4 + e2] = Elem<T>::pack(s0, s1);
-      dsv[e] = s0;
-      dsv[e + 1] = s1;
-    }
-    if (db_ptr != nullptr) {
-      float* dst = db_ptr + ch * 8;
-      if (db_store) {
-        *reinterpret_cast<float4*>(dst) = make_float4(dsv[0], dsv[1], dsv[2], dsv[3]);
-        *reinterpret_cast<float4*>(dst + 4) = make_float4(dsv[4], dsv[5], dsv[6], dsv[7]);
-      } else {
-        red_add_v4(dst, dsv[0], dsv[1], dsv[2], dsv[3]);
-        red_add_v4(dst + 4, dsv[4], dsv[5], dsv[6], dsv[7]);
-      }
+  for (int e2 = 0; e2 < 4; ++e2) {
+    const int e = 2 * e2;
+    const float x0 = fmaf(__uint_as_float(sv[e]), scale, Elem<T>::lo(wb[e2])) + Elem<T>::lo(wm[e2]);
+    const float x1 = fmaf(__uint_as_float(sv[e + 1]), scale, Elem<T>::hi(wb[e2])) + Elem<T>::hi(wm[e2]);
+    const float p0 = ex2f(fmaf(x0, kLog2e, -l8[e]));
+    const float p1 = ex2f(fmaf(x1, kLog2e, -l8[e + 1]));
+    const float s0 = p0 * (__uint_as_float(dpv[e]) - d8[e]);
+    const float s1 = p1 * (__uint_as_float(dpv[e + 1]) - d8[e + 1]);
+    pw[e2] = key_ok ? Elem<T>::pack(p0, p1) : 0u;
+    dw[e2] = key_ok ? Elem<T>::pack(s0, s1) : 0u;
+    dsv[e] = s0;
+    dsv[e + 1] = s1;
+  }
+  if (db_ptr != nullptr) {
+    if (db_store) {
+      *reinterpret_cast<float4*>(db_ptr) = make_float4(dsv[0], dsv[1], dsv[2], dsv[3]);
+      *reinterpret_cast<float4*>(db_ptr + 4) = make_float4(dsv[4], dsv[5], dsv[6], dsv[7]);
+    } else {
+      red_add_v4(db_ptr, dsv[0], dsv[1], dsv[2], dsv[3]);
+      red_add_v4(db_ptr + 4, dsv[4], dsv[5], dsv[6], dsv[7]);
     }
   }
 }
@@ -185,15 +182,19 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   float* rk_arr = reinterpret_cast<float*>(smem_ptr + p.off_rk);
   float* rowstats = reinterpret_cast<float*>(smem_ptr + p.off_rowstats);
   const uint32_t NKV = p.n_kv_stages, NDS = p.n_ds_bufs, NBM = p.n_bm_stages;
-  const uint32_t tm_st = tmem + lane_base + wg * 128u + kTmST;
-  const uint32_t tm_dpt = tmem + lane_base + wg * 128u + kTmDPT;
 
+  // Jobs of a single tile (windows of at most 128 tokens) split the per-job work by kind instead
+  // of by half: warpgroup 1 normalises K and writes dV and dK, warpgroup 0 normalises Q and writes
+  // dQ (the barriers are initialised with the matching arrival counts).
+  const bool single_tile = (g.KB * g.MT == 1);
   // ---- K of a job: normalise in place, remember 1 / |k| ----
   auto prologue_job = [&](const Ring& r) -> bool {
+    // a single tile of keys is left to warpgroup 1 (warpgroup 0 normalises Q meanwhile)
+    if (single_tile && wg == 0) return true;
     const uint32_t kvs = r.stage;
     const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
     if (!mbar_wait(bar(kbKvFull + kvs), r.phase, ctx, 50)) return false;
-    for (uint32_t rr = tid; rr < static_cast<uint32_t>(p.rows_kv); rr += 256u)
+    for (uint32_t rr = single_tile ? lt : tid; rr < static_cast<uint32_t>(p.rows_kv); rr += 256u)
       rk_arr[kvs * p.rows_kv + rr] = normalise_row<T>(k_base, rr);
     fence_proxy_async_smem();
     mbar_arrive(bar(kbKvReady + kvs));
@@ -252,138 +253,162 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
 
   const uint32_t nsets = bwd_num_sets(p, g.KB, g.MT);
   const uint32_t sets_mask = nsets - 1u, sets_shift = nsets - 1u;
-  uint32_t jt = 0, nst = 0, kdkv = 0, kdq = 0;
+  uint32_t jt = 0, kdkv = 0, kdq = 0;
+  uint32_t nst = 0u;   // phase bit per 32-query chunk of my step
   Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS), bm_ring(NBM);
   TraceCursor tr = (lt == 0) ? trace_begin(p.trace, wg == 0 ? 0 : 3) : TraceCursor{nullptr, 0};
   // ---- dK, dV of one key block (thread = key): warpgroup 0 writes dV, warpgroup 1 writes dK ----
   auto dkv_epilogue = [&](const TileIt& it, uint32_t kvs_e, uint32_t kd) -> bool {
-      // dK, dV of key block it.j are complete
-      const uint32_t set = kd & sets_mask, use = kd >> sets_shift;
-      if (!mbar_wait(bar(kbDkvFull + set), use & 1u, ctx, 55)) return false;
-      tc_fence_after();
-      trace_ev(tr, 10);
-      const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
-      const int bw = bwd_bw(p, g, it.t, m);
-      const int jg = g.pair ? static_cast<int>(lt & 63u) : it.j * kTileRows + static_cast<int>(lt);
-      const bool ok = bw < p.BW && jg < g.N;
-      uint32_t r[32];
-      tmem_ld32(tmem + lane_base + (wg == 0 ? tm_dv(set) : tm_dk(set)), r);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar(kbDkvFree + set));
-      if (wg == 0) {
+    if (single_tile && wg == 0) return true;
+    // dK, dV of key block it.j are complete
+    const uint32_t set = kd & sets_mask, use = kd >> sets_shift;
+    if (!mbar_wait(bar(kbDkvFull + set), use & 1u, ctx, 55)) return false;
+    tc_fence_after();
+    trace_ev(tr, 10);
+    const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
+    const int bw = bwd_bw(p, g, it.t, m);
+    const int jg = g.pair ? static_cast<int>(lt & 63u) : it.j * kTileRows + static_cast<int>(lt);
+    const bool ok = bw < p.BW && jg < g.N;
+    // (rolled loops over groups of eight columns: see bwd_group about code size)
+    if (wg == 0 || single_tile) {
+      uint16_t* dst = static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + jg * p.dv_sn;
+      const uint32_t t_dv = tmem + lane_base + tm_dv(set);
+#pragma unroll 1
+      for (uint32_t gq = 0; gq < 4u; ++gq) {
+        uint32_t r[8];
+        tmem_ld8(t_dv + 8u * gq, r);
+        tmem_wait_ld();
         if (ok) {
-          uint16_t* dst = static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + jg * p.dv_sn;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint4 v;
-            v.x = Elem<T>::pack(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
-            v.y = Elem<T>::pack(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
-            v.z = Elem<T>::pack(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
-            v.w = Elem<T>::pack(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
-            *reinterpret_cast<uint4*>(dst + ch * 8) = v;
-          }
-        }
-      } else {
-        // dk = scale * (dK' - k^ (k^ . dK')) / |k|
-        const uint32_t krow = g.pair ? lt : static_cast<uint32_t>(it.j) * kTileRows + lt;
-        const uint32_t k_base = smem_base + p.off_kv + kvs_e * p.kv_stage_bytes;
-        float kh[32];
-        float dot = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t w[4];
-          lds128(k_base + sw64_offset(krow, ch), w);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            kh[ch * 8 + 2 * i] = Elem<T>::lo(w[i]);
-            kh[ch * 8 + 2 * i + 1] = Elem<T>::hi(w[i]);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) dot = fmaf(kh[i], __uint_as_float(r[i]), dot);
-        const float f = scale * rk_arr[kvs_e * p.rows_kv + krow];
-        if (ok) {
-          uint16_t* dst = static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + jg * p.dk_sn;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            float o8[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              o8[i] = f * (__uint_as_float(r[ch * 8 + i]) - kh[ch * 8 + i] * dot);
-            uint4 v;
-            v.x = Elem<T>::pack(o8[0], o8[1]);
-            v.y = Elem<T>::pack(o8[2], o8[3]);
-            v.z = Elem<T>::pack(o8[4], o8[5]);
-            v.w = Elem<T>::pack(o8[6], o8[7]);
-            *reinterpret_cast<uint4*>(dst + ch * 8) = v;
-          }
+          uint4 v;
+          v.x = Elem<T>::pack(__uint_as_float(r[0]), __uint_as_float(r[1]));
+          v.y = Elem<T>::pack(__uint_as_float(r[2]), __uint_as_float(r[3]));
+          v.z = Elem<T>::pack(__uint_as_float(r[4]), __uint_as_float(r[5]));
+          v.w = Elem<T>::pack(__uint_as_float(r[6]), __uint_as_float(r[7]));
+          *reinterpret_cast<uint4*>(dst + 8u * gq) = v;
         }
       }
-      if (it.j == g.KB - 1) mbar_arrive(bar(kbKvFree + kvs_e));   // K^ in shared memory no longer needed
-      trace_ev(tr, 11);
-
+      if (wg == 0) {
+        tc_fence_before();
+        mbar_arrive(bar(kbDkvFree + set));
+      }
+    }
+    if (wg == 1) {
+      // dk = scale * (dK' - k^ (k^ . dK')) / |k|: one pass for the dot product, one for the output
+      const uint32_t krow = g.pair ? lt : static_cast<uint32_t>(it.j) * kTileRows + lt;
+      const uint32_t k_row = smem_base + p.off_kv + kvs_e * p.kv_stage_bytes + krow * 64u;
+      const uint32_t k_sw = (krow >> 1) & 3u;
+      const uint32_t t_dk = tmem + lane_base + tm_dk(set);
+      float dot = 0.f;
+#pragma unroll 1
+      for (uint32_t gq = 0; gq < 4u; ++gq) {
+        uint32_t r[8], w[4];
+        tmem_ld8(t_dk + 8u * gq, r);
+        lds128(k_row + ((gq ^ k_sw) << 4), w);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          dot = fmaf(Elem<T>::lo(w[i]), __uint_as_float(r[2 * i]), dot);
+          dot = fmaf(Elem<T>::hi(w[i]), __uint_as_float(r[2 * i + 1]), dot);
+        }
+      }
+      const float f = scale * rk_arr[kvs_e * p.rows_kv + krow];
+      uint16_t* dst = static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + jg * p.dk_sn;
+#pragma unroll 1
+      for (uint32_t gq = 0; gq < 4u; ++gq) {
+        uint32_t r[8], w[4];
+        tmem_ld8(t_dk + 8u * gq, r);
+        lds128(k_row + ((gq ^ k_sw) << 4), w);
+        tmem_wait_ld();
+        if (ok) {
+          float o8[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            o8[2 * i] = f * (__uint_as_float(r[2 * i]) - Elem<T>::lo(w[i]) * dot);
+            o8[2 * i + 1] = f * (__uint_as_float(r[2 * i + 1]) - Elem<T>::hi(w[i]) * dot);
+          }
+          uint4 v;
+          v.x = Elem<T>::pack(o8[0], o8[1]);
+          v.y = Elem<T>::pack(o8[2], o8[3]);
+          v.z = Elem<T>::pack(o8[4], o8[5]);
+          v.w = Elem<T>::pack(o8[6], o8[7]);
+          *reinterpret_cast<uint4*>(dst + 8u * gq) = v;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar(kbDkvFree + set));
+    }
+    if (it.j == g.KB - 1) mbar_arrive(bar(kbKvFree + kvs_e));   // K^ in shared memory no longer needed
+    trace_ev(tr, 11);
     return true;
   };
   // ---- dQ of a job (thread = query): warpgroup (i mod 2) writes query tile i ----
   auto dq_epilogue = [&](int t_e, uint32_t kq) -> bool {
-        // dQ of every query tile of the job is complete
-        const uint32_t set = kq & sets_mask, use = kq >> sets_shift;
-        if (!mbar_wait(bar(kbDqFull + set), use & 1u, ctx, 56)) return false;
-        tc_fence_after();
-        trace_ev(tr, 12);
-        for (int i = static_cast<int>(wg); i < g.MT; i += 2) {
-          const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
-          const int bwq = bwd_bw(p, g, t_e, mq);
-          const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
-          const bool okq = bwq < p.BW && ig < g.N;
-          uint32_t rq[32];
-          tmem_ld32(tmem + lane_base + tm_dq(nsets, set, static_cast<uint32_t>(i)), rq);
-          tmem_wait_ld();
-          if (okq) {
-            const uint16_t* qrow = static_cast<const uint16_t*>(p.q) + bwq * p.q_sbw + g.h * p.q_sh + ig * p.q_sn;
-            float qv[32];
-            float ss = 0.f;
+    if (single_tile && wg == 1) return true;
+    // dQ of every query tile of the job is complete
+    const uint32_t set = kq & sets_mask, use = kq >> sets_shift;
+    if (!mbar_wait(bar(kbDqFull + set), use & 1u, ctx, 56)) return false;
+    tc_fence_after();
+    trace_ev(tr, 12);
+    const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
+    const int bwq = bwd_bw(p, g, t_e, mq);
+#pragma unroll 1
+    for (int i = static_cast<int>(wg); i < g.MT; i += 2) {
+      const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
+      const bool okq = bwq < p.BW && ig < g.N;
+      const uint32_t t_dq = tmem + lane_base + tm_dq(nsets, set, static_cast<uint32_t>(i));
+      // dq = scale * (dQ' - q^ (q^ . dQ')) / |q| from the raw q row: with q^ = q / |q| the dot
+      // product is (q . dQ') / |q|, so one pass gives |q| and the dot product, a second the output.
+      // Every lane runs both loops (the tensor-memory loads are warp-wide); only the global
+      // accesses are predicated.
+      const uint16_t* qrow = static_cast<const uint16_t*>(p.q) + bwq * p.q_sbw + g.h * p.q_sh + ig * p.q_sn;
+      float ss = 0.f, qd = 0.f;
+#pragma unroll 1
+      for (uint32_t gq = 0; gq < 4u; ++gq) {
+        uint32_t r[8];
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (okq) v = ldg_nc_v4(qrow + 8u * gq);
+        tmem_ld8(t_dq + 8u * gq, r);
+        tmem_wait_ld();
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-              const uint4 v = ldg_nc_v4(qrow + ch * 8);
-              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                qv[ch * 8 + 2 * e] = Elem<T>::lo(w[e]);
-                qv[ch * 8 + 2 * e + 1] = Elem<T>::hi(w[e]);
-              }
-            }
-#pragma unroll
-            for (int e = 0; e < 32; ++e) ss = fmaf(qv[e], qv[e], ss);
-            const float rn = rsqrtf(fmaxf(ss, 1e-24f));
-            float dot = 0.f;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              qv[e] *= rn;
-              dot = fmaf(qv[e], __uint_as_float(rq[e]), dot);
-            }
-            dscale_acc += dot;
-            const float f = scale * rn;
-            uint16_t* dst = static_cast<uint16_t*>(p.dq) + bwq * p.dq_sbw + g.h * p.dq_sh + ig * p.dq_sn;
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-              float o8[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                o8[e] = f * (__uint_as_float(rq[ch * 8 + e]) - qv[ch * 8 + e] * dot);
-              uint4 v;
-              v.x = Elem<T>::pack(o8[0], o8[1]);
-              v.y = Elem<T>::pack(o8[2], o8[3]);
-              v.z = Elem<T>::pack(o8[4], o8[5]);
-              v.w = Elem<T>::pack(o8[6], o8[7]);
-              *reinterpret_cast<uint4*>(dst + ch * 8) = v;
-            }
-          }
+        for (int e = 0; e < 4; ++e) {
+          const float a = Elem<T>::lo(w[e]), b = Elem<T>::hi(w[e]);
+          ss = fmaf(a, a, ss);
+          ss = fmaf(b, b, ss);
+          qd = fmaf(a, __uint_as_float(r[2 * e]), qd);
+          qd = fmaf(b, __uint_as_float(r[2 * e + 1]), qd);
         }
-        tc_fence_before();
-        mbar_arrive(bar(kbDqFree + set));
-        trace_ev(tr, 13);
+      }
+      const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+      const float dot = qd * rn;
+      if (okq) dscale_acc += dot;
+      const float f = scale * rn, cq = rn * dot;
+      uint16_t* dst = static_cast<uint16_t*>(p.dq) + bwq * p.dq_sbw + g.h * p.dq_sh + ig * p.dq_sn;
+#pragma unroll 1
+      for (uint32_t gq = 0; gq < 4u; ++gq) {
+        uint32_t r[8];
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (okq) v = ldg_nc_v4(qrow + 8u * gq);
+        tmem_ld8(t_dq + 8u * gq, r);
+        tmem_wait_ld();
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        float o8[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          o8[2 * e] = f * (__uint_as_float(r[2 * e]) - Elem<T>::lo(w[e]) * cq);
+          o8[2 * e + 1] = f * (__uint_as_float(r[2 * e + 1]) - Elem<T>::hi(w[e]) * cq);
+        }
+        uint4 o;
+        o.x = Elem<T>::pack(o8[0], o8[1]);
+        o.y = Elem<T>::pack(o8[2], o8[3]);
+        o.z = Elem<T>::pack(o8[4], o8[5]);
+        o.w = Elem<T>::pack(o8[6], o8[7]);
+        if (okq) *reinterpret_cast<uint4*>(dst + 8u * gq) = o;
+      }
+    }
+    tc_fence_before();
+    mbar_arrive(bar(kbDqFree + set));
+    trace_ev(tr, 13);
     return true;
   };
   bool pend_dkv = false, pend_dq = false;
@@ -426,48 +451,68 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     }
 
     trace_ev(tr, 2);
-    // ------------------------------ my step of the current tile ------------------------------
-    const int nr = step_rows(g, cur.i, static_cast<int>(wg));
+    // ------------------------------ my share of the current tile ------------------------------
+    // Windows of more than 64 tokens: warpgroup w takes step w (queries [64 w, 64 w + 64)) in two
+    // chunks.  Pair mode: only the diagonal blocks (keys and queries of the same unit) carry work,
+    // so the warps whose lanes hold the keys of unit m take the queries of unit m (step m), and
+    // the two warpgroups split them: warpgroup w takes chunk w.  The off-diagonal block of the
+    // same lanes and chunk in the other step is filled with zeros.
+    const uint32_t um = lt >> 6;                       // pair mode: unit of my key
+    const uint32_t step = g.pair ? um : wg;
+    const int nr = step_rows(g, cur.i, static_cast<int>(step));
     const uint32_t kvs = kv_ring.stage;
     if (nr > 0) {
       bool key_ok;
       int jg;
       if (g.pair) {
-        const int m = static_cast<int>(lt >> 6);
-        key_ok = (m == static_cast<int>(wg)) && bwd_bw(p, g, cur.t, m) < p.BW &&
-                 static_cast<int>(lt & 63u) < g.N;
+        key_ok = bwd_bw(p, g, cur.t, static_cast<int>(um)) < p.BW && static_cast<int>(lt & 63u) < g.N;
         jg = static_cast<int>(lt & 63u);
       } else {
         jg = cur.j * kTileRows + static_cast<int>(lt);
         key_ok = jg < g.N;
       }
-      if (!mbar_wait(bar(kbStFull + wg), nst & 1u, ctx, 52)) return;
-      trace_ev(tr, 3);
       const uint32_t dsb = ds_ring.stage;
       if (!mbar_wait(bar(kbDsFree + dsb), ds_ring.phase ^ 1u, ctx, 53)) return;
-      tc_fence_after();
       trace_ev(tr, 4);
-      const uint32_t ds_slab = smem_base + p.off_ds + dsb * kDsTileBytes + wg * 16384u;
+      const uint32_t ds_tile = smem_base + p.off_ds + dsb * kDsTileBytes;
+      const uint32_t ds_slab = ds_tile + step * 16384u;
       const uint32_t qs = qdo_ring.stage;
-      const float* lse2 = rowstats + qs * 256u + wg * 64u;
-      const float* delta = rowstats + qs * 256u + 128u + wg * 64u;
-      const long long db_buf = g.pair ? 2ll * blockIdx.x + wg : static_cast<long long>(blockIdx.x);
+      const float* lse2 = rowstats + qs * 256u + step * 64u;
+      const float* delta = rowstats + qs * 256u + 128u + step * 64u;
+      const long long db_buf = g.pair ? 2ll * blockIdx.x + um : static_cast<long long>(blockIdx.x);
       const int ig0 = g.pair ? 0 : cur.i * kTileRows + static_cast<int>(wg) * kStepCols;
       float* db_row = (p.db_partial != nullptr && key_ok)
                           ? p.db_partial + db_buf * p.db_buf_stride + static_cast<long long>(jg) * p.db_pitch + ig0
                           : nullptr;
       const bool db_store = (jt == 0);
+      const uint32_t tm_st = tmem + lane_base + step * 128u + kTmST;
+      const uint32_t tm_dpt = tmem + lane_base + step * 128u + kTmDPT;
+      const int c_first = g.pair ? static_cast<int>(wg) : 0, c_last = g.pair ? static_cast<int>(wg) : 1;
 
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pw[16], dw[16];
+      for (int c = c_first; c <= c_last; ++c) {
         const int rows_left = nr - kChunkCols * c;
         if (rows_left > 0) {
-          uint32_t sv[32], dpv[32];
-          tmem_ld32(tm_st + 32u * c, sv);
-          tmem_ld32(tm_dpt + 32u * c, dpv);
-          tmem_wait_ld();
-          trace_ev(tr, 5);
+          // scores of this chunk (the tensor core is meanwhile working on the other chunks)
+          if (!mbar_wait(bar(kbStFull + 2 * step + c), (nst >> c) & 1u, ctx, 52)) return;
+          tc_fence_after();
+          trace_ev(tr, 3);
+          if (g.pair) {
+            // the other unit's queries must not see my key: zeros in the other step, same chunk
+            // (issued now, so that the stores drain while this chunk is being computed)
+            const uint32_t other = step ^ 1u;
+            if (!mbar_wait(bar(kbStFull + 2 * other + c), (nst >> c) & 1u, ctx, 57)) return;
+            tc_fence_after();
+            uint32_t z[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) z[i] = 0u;
+            tmem_st16(tmem + lane_base + other * 128u + kTmST + 32u * c, z);
+            tmem_st16(tmem + lane_base + other * 128u + kTmDPT + 32u * c, z);
+            const uint32_t z4[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd)
+              sts128(ds_tile + other * 16384u + sw128_offset(lt, 4u * c + qd), z4);
+          }
           uint32_t bias_tile = 0, mask_tile = 0;
           const uint32_t st = bm_ring.stage;
           if (any_table) {
@@ -476,40 +521,62 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
             if (!mbar_wait(bar(kbBmFull + 2 * wg + st), bm_ring.phase, ctx, 54)) return;
           }
           trace_ev(tr, 6);
+          // pair mode: one bias box serves both units (same head), the mask has a box per unit
+          const uint32_t bias_row = g.pair ? (lt & 63u) : lt;
+          const uint32_t bias_base = bias_tile + bias_row * 64u, bias_sw = (bias_row >> 1) & 3u;
+          const uint32_t mask_base = mask_tile + lt * 64u, mask_sw = (lt >> 1) & 3u;
+          const uint32_t ds_base = ds_slab + lt * 128u, ds_sw = lt & 7u;
+          const uint32_t t_s = tm_st + 32u * c, t_d = tm_dpt + 32u * c;
+          const float* lse2_c = lse2 + 32 * c;
+          const float* delta_c = delta + 32 * c;
           float* dbp = db_row != nullptr ? db_row + kChunkCols * c : nullptr;
-          if (rows_left >= kChunkCols)
-            bwd_chunk<T, false>(p.has_bias, p.has_mask, sv, dpv, bias_tile, mask_tile, lt,
-                                lse2 + 32 * c, delta + 32 * c, scale, rows_left, dbp, db_store, pw, dw);
-          else
-            bwd_chunk<T, true>(p.has_bias, p.has_mask, sv, dpv, bias_tile, mask_tile, lt,
-                               lse2 + 32 * c, delta + 32 * c, scale, rows_left, dbp, db_store, pw, dw);
+          // four groups of eight queries, two per trip; the scores of the next group are fetched
+          // from tensor memory while the current one is computed
+          uint32_t sa[8], da[8], sb[8], db8[8];
+          tmem_ld8(t_s, sa);
+          tmem_ld8(t_d, da);
+#pragma unroll 1
+          for (uint32_t gq = 0; gq < 4u; gq += 2u) {
+            uint32_t pw[4], dw[4];
+            tmem_wait_ld();
+            tmem_ld8(t_s + 8u * (gq + 1u), sb);
+            tmem_ld8(t_d + 8u * (gq + 1u), db8);
+            bwd_group<T>(p.has_bias, p.has_mask, sa, da, bias_base + ((gq ^ bias_sw) << 4),
+                         mask_base + ((gq ^ mask_sw) << 4), lse2_c + 8u * gq, delta_c + 8u * gq, scale,
+                         key_ok, dbp != nullptr ? dbp + 8u * gq : nullptr, db_store, pw, dw);
+            // P^T and dS^T go back over the first 16 columns of this chunk's own S^T / dP^T columns
+            tmem_st4(t_s + 4u * gq, pw);
+            tmem_st4(t_d + 4u * gq, dw);
+            sts128(ds_base + (((4u * c + gq) ^ ds_sw) << 4), dw);
+            tmem_wait_ld();
+            if (gq + 2u < 4u) {
+              tmem_ld8(t_s + 8u * (gq + 2u), sa);
+              tmem_ld8(t_d + 8u * (gq + 2u), da);
+            }
+            bwd_group<T>(p.has_bias, p.has_mask, sb, db8, bias_base + (((gq + 1u) ^ bias_sw) << 4),
+                         mask_base + (((gq + 1u) ^ mask_sw) << 4), lse2_c + 8u * (gq + 1u),
+                         delta_c + 8u * (gq + 1u), scale, key_ok,
+                         dbp != nullptr ? dbp + 8u * (gq + 1u) : nullptr, db_store, pw, dw);
+            tmem_st4(t_s + 4u * (gq + 1u), pw);
+            tmem_st4(t_d + 4u * (gq + 1u), dw);
+            sts128(ds_base + (((4u * c + gq + 1u) ^ ds_sw) << 4), dw);
+          }
           trace_ev(tr, 7);
           if (any_table) {
             mbar_arrive(bar(kbBmFree + 2 * wg + st));
             bm_ring.advance();
           }
-          if (!key_ok) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { pw[i] = 0u; dw[i] = 0u; }
-          }
         } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) { pw[i] = 0u; dw[i] = 0u; }
+          continue;   // no query of this chunk exists: nobody issues or reads anything for it
         }
-        tmem_st16(tm_st + 16u * c, pw);
-        tmem_st16(tm_dpt + 16u * c, dw);
-#pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-          const uint32_t w4[4] = {dw[qd * 4], dw[qd * 4 + 1], dw[qd * 4 + 2], dw[qd * 4 + 3]};
-          sts128(ds_slab + sw128_offset(lt, 4u * c + qd), w4);
-        }
+        tmem_wait_st();
+        tc_fence_before();
+        fence_proxy_async_smem();
+        mbar_arrive(bar(kbPtFull + 2 * step + c));
+        if (g.pair) mbar_arrive(bar(kbPtFull + 2 * (step ^ 1u) + c));
+        nst ^= 1u << c;
         trace_ev(tr, 8);
       }
-      tmem_wait_st();
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(bar(kbPtFull + wg));
-      ++nst;
       trace_ev(tr, 9);
     }
 
@@ -592,37 +659,41 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
     b.dO = b.q + 2u * kBoxBytes;
     return b;
   };
-  // S^T = K^ Q^^T and dP^T = V dO^T for step w of a tile
-  auto issue_sdp = [&](const TileIt& it, int w, const Bases& b) {
-    const int nr = step_rows(g, it.i, w);
-    const uint32_t n16 = static_cast<uint32_t>(min(kStepCols, ((nr + 15) / 16) * 16));
+  // S^T = K^ Q^^T and dP^T = V dO^T for the 32-query chunk c of step w of a tile.  All 32 columns
+  // are always computed: query rows past the end of the window are zeros in shared memory.
+  const uint32_t idesc_s = make_idesc(fmt, 128, kChunkCols, 0, 0);
+  auto issue_sdp = [&](const TileIt& it, int w, int c, const Bases& b) {
     const uint32_t key_off = g.pair ? 0u : static_cast<uint32_t>(it.j) * (kTileRows * kRowBytes);
-    const uint32_t row_off = static_cast<uint32_t>(w) * (kStepCols * kRowBytes);
-    const uint32_t idesc = make_idesc(fmt, 128, n16, 0, 0);
-    const uint32_t st = tmem + w * 128u + kTmST, dpt = tmem + w * 128u + kTmDPT;
+    const uint32_t row_off = static_cast<uint32_t>(w * kStepCols + c * kChunkCols) * kRowBytes;
+    const uint32_t st = tmem + w * 128u + kTmST + 32u * c, dpt = tmem + w * 128u + kTmDPT + 32u * c;
     // the two accumulation chains are interleaved: back-to-back MMAs into one accumulator wait
     // for each other
-    mma_ss(st, desc_at(dk64, b.k + key_off), desc_at(dk64, b.q + row_off), idesc, 0u);
-    mma_ss(dpt, desc_at(dk64, b.v + key_off), desc_at(dk64, b.dO + row_off), idesc, 0u);
-    mma_ss(st, desc_at(dk64, b.k + key_off + 32u), desc_at(dk64, b.q + row_off + 32u), idesc, 1u);
-    mma_ss(dpt, desc_at(dk64, b.v + key_off + 32u), desc_at(dk64, b.dO + row_off + 32u), idesc, 1u);
-    mma_commit(bar(kbStFull + w));
+#pragma unroll 1
+    for (uint32_t k = 0; k < 2u; ++k) {
+      mma_ss(st, desc_at(dk64, b.k + key_off + 32u * k), desc_at(dk64, b.q + row_off + 32u * k), idesc_s, k);
+      mma_ss(dpt, desc_at(dk64, b.v + key_off + 32u * k), desc_at(dk64, b.dO + row_off + 32u * k), idesc_s, k);
+    }
+    mma_commit(bar(kbStFull + 2 * w + c));
   };
 
   uint32_t kdkv = 0, kdq = 0;
   const uint32_t nsets = bwd_num_sets(p, g.KB, g.MT);
   const uint32_t sets_mask = nsets - 1u, sets_shift = nsets - 1u;
   TraceCursor tr = trace_begin(p.trace, 1);
-  uint32_t nst[2] = {0u, 0u};
+  uint32_t nst = 0u;   // phase bit per (2 * warpgroup + chunk)
   Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS);
   TileIt cur{0, 0, 0};
+  auto chunk_exists = [&](const TileIt& it, int w, int c) { return step_rows(g, it.i, w) - kChunkCols * c > 0; };
   if (!mbar_wait(bar(kbKvReady + 0), 0u, ctx, 60)) return;
   if (!mbar_wait(bar(kbQdoReady + 0), 0u, ctx, 61)) return;
   tc_fence_after();
   {
     const Bases b0 = stage_bases(kv_ring, qdo_ring);
-    for (int w = 0; w < 2; ++w)
-      if (step_rows(g, cur.i, w) > 0) issue_sdp(cur, w, b0);
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c)
+#pragma unroll 1
+      for (int w = 0; w < 2; ++w)
+        if (chunk_exists(cur, w, c)) issue_sdp(cur, w, c, b0);
   }
 
   while (true) {
@@ -645,34 +716,41 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
         if (!mbar_wait(bar(kbDqFree + (kdq & sets_mask)), ((kdq >> sets_shift) & 1u) ^ 1u, ctx, 63)) return;
       }
     }
-    for (int w = 0; w < 2; ++w) {
-      if (step_rows(g, cur.i, w) > 0) {
-        if (!mbar_wait(bar(kbPtFull + w), nst[w] & 1u, ctx, 64)) return;
-        ++nst[w];
-        tc_fence_after();
-        trace_ev(tr, 30 + w);
-        const uint32_t row_off = static_cast<uint32_t>(w) * (kStepCols * kRowBytes);
-        const uint32_t first = (cur.i > 0 || w > 0) ? 1u : 0u;
-        const uint32_t a_p = tmem + w * 128u + kTmST, a_ds = tmem + w * 128u + kTmDPT;
-#pragma unroll
-        for (uint32_t k = 0; k < 4; ++k) {
-          mma_ts(tmem + tm_dv(kdkv & sets_mask), a_p + k * 8u, desc_at(dm64, b.dO + row_off + k * 1024u),
-                 idesc_acc, first | k);
-          mma_ts(tmem + tm_dk(kdkv & sets_mask), a_ds + k * 8u, desc_at(dm64, b.q + row_off + k * 1024u),
-                 idesc_acc, first | k);
-        }
-      }
-      trace_ev(tr, 32 + w);
-      if (look_now) {
-        if (w == 0) {
-          if (cross) {
-            if (!mbar_wait(bar(kbKvReady + kv_next.stage), kv_next.phase, ctx, 65)) return;
-          }
-          if (!mbar_wait(bar(kbQdoReady + qdo_next.stage), qdo_next.phase, ctx, 66)) return;
+    // chunks in the order in which the two warpgroups finish them: (w0,c0) (w1,c0) (w0,c1) (w1,c1)
+    bool looked = false;
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll 1
+      for (int w = 0; w < 2; ++w) {
+        if (chunk_exists(cur, w, c)) {
+          const int bi = 2 * w + c;
+          if (!mbar_wait(bar(kbPtFull + bi), (nst >> bi) & 1u, ctx, 64)) return;
+          nst ^= 1u << bi;
           tc_fence_after();
+          trace_ev(tr, 30 + bi);
+          const uint32_t row_off = static_cast<uint32_t>(w * kStepCols + c * kChunkCols) * kRowBytes;
+          const uint32_t first = (cur.i > 0 || w > 0 || c > 0) ? 1u : 0u;
+          const uint32_t a_p = tmem + w * 128u + kTmST + 32u * c, a_ds = tmem + w * 128u + kTmDPT + 32u * c;
+#pragma unroll 1
+          for (uint32_t k = 0; k < 2; ++k) {
+            mma_ts(tmem + tm_dv(kdkv & sets_mask), a_p + k * 8u, desc_at(dm64, b.dO + row_off + k * 1024u),
+                   idesc_acc, first | k);
+            mma_ts(tmem + tm_dk(kdkv & sets_mask), a_ds + k * 8u, desc_at(dm64, b.q + row_off + k * 1024u),
+                   idesc_acc, first | k);
+          }
         }
-        if (step_rows(g, nxt.i, w) > 0) issue_sdp(nxt, w, bn);
-        trace_ev(tr, 34 + w);
+        if (look_now) {
+          if (!looked) {
+            if (cross) {
+              if (!mbar_wait(bar(kbKvReady + kv_next.stage), kv_next.phase, ctx, 65)) return;
+            }
+            if (!mbar_wait(bar(kbQdoReady + qdo_next.stage), qdo_next.phase, ctx, 66)) return;
+            tc_fence_after();
+            looked = true;
+          }
+          if (chunk_exists(nxt, w, c)) issue_sdp(nxt, w, c, bn);
+          trace_ev(tr, 34 + w);
+        }
       }
     }
     // dQ^ of query tile cur.i += dS K^ (key block cur.j)
@@ -681,7 +759,7 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
       const uint32_t kb = b.k + (g.pair ? 0u : static_cast<uint32_t>(cur.j) * (kTileRows * kRowBytes));
       const uint32_t dq_col = tmem + tm_dq(nsets, kdq & sets_mask, static_cast<uint32_t>(cur.i));
       const uint32_t first = cur.j > 0 ? 1u : 0u;
-#pragma unroll
+#pragma unroll 1
       for (uint32_t k = 0; k < 8; ++k)
         mma_ss(dq_col, desc_at(dds, ds_base + k * 2048u), desc_at(dm64, kb + k * 1024u), idesc_dq, first | k);
     }
@@ -702,8 +780,11 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
       if (!mbar_wait(bar(kbKvReady + kv_next.stage), kv_next.phase, ctx, 67)) return;
       if (!mbar_wait(bar(kbQdoReady + qdo_next.stage), qdo_next.phase, ctx, 68)) return;
       tc_fence_after();
-      for (int w = 0; w < 2; ++w)
-        if (step_rows(g, nxt.i, w) > 0) issue_sdp(nxt, w, bn);
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c)
+#pragma unroll 1
+        for (int w = 0; w < 2; ++w)
+          if (chunk_exists(nxt, w, c)) issue_sdp(nxt, w, c, bn);
     }
     kv_ring = kv_next;
     qdo_ring = qdo_next;
@@ -713,151 +794,96 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
 }
 
 // ------------------------------------------------------------------------------------------------
-// TMA producer (one thread): three independent streams, none of which ever blocks the others.
-//   (a)  K/V of a job, then Q/dO of each of its tiles
-//   (b0) bias^T / mask^T chunks for warpgroup 0     (b1) the same for warpgroup 1
+// TMA producers: three warps (one thread each), one stream each, so that none of them ever waits
+// for the consumers of another and each is a short loop of blocking waits:
+//   warp 9   K/V of a job, then Q/dO of each of its tiles
+//   warp 10  bias^T / mask^T chunks for warpgroup 0        warp 11  the same for warpgroup 1
+// Every stream issues its loads in the order in which they are consumed.
 // ------------------------------------------------------------------------------------------------
-struct BmCursor {
-  TileIt it;
-  int c;
-  uint32_t stage, phase;
-  bool done;
-};
-
-__device__ void bwd_load_role(const BwdParams& p, uint32_t smem_base, uint32_t bars,
-                              const WaitCtx& ctx) {
+__device__ void bwd_load_main(const BwdParams& p, uint32_t smem_base, uint32_t bars, const WaitCtx& ctx) {
   const BwdGeom g = bwd_geom(p);
   if (g.njobs == 0) return;
   auto bar = [&](int i) { return bars + 8u * i; };
-  const uint32_t NKV = p.n_kv_stages, NBM = p.n_bm_stages;
-  const bool any_table = p.has_bias || p.has_mask;
-  const uint32_t ntab = (p.has_bias ? 1u : 0u) + (p.has_mask ? 1u : 0u);
-
-  // stream (a)
-  TileIt a_it{0, 0, 0};
-  bool a_kv_pending = true, a_done = false;
-  Ring a_kv(NKV), a_qdo(kNumQdoStages);
-  // streams (b0), (b1)
-  BmCursor bc[2];
-  auto bm_seek = [&](BmCursor& b, int w) {
-    // move to the next existing (step, chunk) at or after the current position
-    while (!b.done) {
-      const int nr = step_rows(g, b.it.i, w);
-      if (nr > 0 && nr - kChunkCols * b.c > 0 && b.c < 2) return;
-      b.c = 0;
-      if (!tile_next(g, b.it)) b.done = true;
-      else if (step_rows(g, b.it.i, w) > 0) return;
-    }
-  };
-  for (int w = 0; w < 2; ++w) {
-    bc[w].it = TileIt{0, 0, 0};
-    bc[w].c = 0;
-    bc[w].stage = 0;
-    bc[w].phase = 0;
-    bc[w].done = !any_table;
-    if (!bc[w].done) bm_seek(bc[w], w);
-  }
-
-  long long t0 = clock64();
-  uint32_t idle = 0;
-  while (!a_done || !bc[0].done || !bc[1].done) {
-    bool progress = false;
-    if (!a_done) {
-      if (a_kv_pending) {
-        const uint32_t kvs = a_kv.stage;
-        if (mbar_test_wait(bar(kbKvFree + kvs), a_kv.phase ^ 1u)) {
-          const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
-          const uint32_t v_base = k_base + static_cast<uint32_t>(p.rows_kv) * kRowBytes;
-          const uint32_t full = bar(kbKvFull + kvs);
-          mbar_arrive_expect_tx(full, 2u * static_cast<uint32_t>(p.rows_kv) * kRowBytes);
-          const int nbox = p.rows_kv / kBoxRows;
-          for (int b = 0; b < nbox; ++b) {
-            const int bw = g.pair ? bwd_bw(p, g, a_it.t, b) : bwd_bw(p, g, a_it.t, 0);
-            const int r0 = g.pair ? 0 : b * kBoxRows;
-            tma_load_4d(k_base + b * kBoxBytes, &p.tm_k, full, 0, r0, g.h, bw);
-            tma_load_4d(v_base + b * kBoxBytes, &p.tm_v, full, 0, r0, g.h, bw);
-          }
-          a_kv_pending = false;
-          progress = true;
-        }
-      } else {
-        const uint32_t qs = a_qdo.stage;
-        if (mbar_test_wait(bar(kbQdoFree + qs), a_qdo.phase ^ 1u)) {
-          const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
-          const uint32_t full = bar(kbQdoFull + qs);
-          mbar_arrive_expect_tx(full, kQdoStageBytes);
-          for (int b = 0; b < 2; ++b) {
-            const int bw = g.pair ? bwd_bw(p, g, a_it.t, b) : bwd_bw(p, g, a_it.t, 0);
-            const int r0 = g.pair ? 0 : a_it.i * kTileRows + b * kBoxRows;
-            tma_load_4d(q_base + b * kBoxBytes, &p.tm_q, full, 0, r0, g.h, bw);
-            tma_load_4d(q_base + 2u * kBoxBytes + b * kBoxBytes, &p.tm_do, full, 0, r0, g.h, bw);
-          }
-          a_qdo.advance();
-          const int t_before = a_it.t;
-          if (!tile_next(g, a_it)) {
-            a_done = true;
-          } else if (a_it.t != t_before) {
-            a_kv.advance();
-            a_kv_pending = true;
-          }
-          progress = true;
-        }
+  TileIt it{0, 0, 0};
+  Ring kv(p.n_kv_stages), qdo(kNumQdoStages);
+  bool new_job = true;
+#pragma unroll 1
+  while (true) {
+    if (new_job) {
+      const uint32_t kvs = kv.stage;
+      if (!mbar_wait(bar(kbKvFree + kvs), kv.phase ^ 1u, ctx, 70)) return;
+      const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
+      const uint32_t v_base = k_base + static_cast<uint32_t>(p.rows_kv) * kRowBytes;
+      const uint32_t full = bar(kbKvFull + kvs);
+      mbar_arrive_expect_tx(full, 2u * static_cast<uint32_t>(p.rows_kv) * kRowBytes);
+      const int nbox = p.rows_kv / kBoxRows;
+#pragma unroll 1
+      for (int b = 0; b < nbox; ++b) {
+        const int bw = bwd_bw(p, g, it.t, g.pair ? b : 0);
+        const int r0 = g.pair ? 0 : b * kBoxRows;
+        tma_load_4d(k_base + b * kBoxBytes, &p.tm_k, full, 0, r0, g.h, bw);
+        tma_load_4d(v_base + b * kBoxBytes, &p.tm_v, full, 0, r0, g.h, bw);
       }
     }
-    for (int w = 0; w < 2; ++w) {
-      BmCursor& b = bc[w];
-      if (b.done) continue;
-      const uint32_t st = b.stage;
-      if (!mbar_test_wait(bar(kbBmFree + 2 * w + st), b.phase ^ 1u)) continue;
+    {
+      const uint32_t qs = qdo.stage;
+      if (!mbar_wait(bar(kbQdoFree + qs), qdo.phase ^ 1u, ctx, 71)) return;
+      const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
+      const uint32_t full = bar(kbQdoFull + qs);
+      mbar_arrive_expect_tx(full, kQdoStageBytes);
+#pragma unroll 1
+      for (int b = 0; b < 2; ++b) {
+        const int bw = bwd_bw(p, g, it.t, g.pair ? b : 0);
+        const int r0 = g.pair ? 0 : it.i * kTileRows + b * kBoxRows;
+        tma_load_4d(q_base + b * kBoxBytes, &p.tm_q, full, 0, r0, g.h, bw);
+        tma_load_4d(q_base + 2u * kBoxBytes + b * kBoxBytes, &p.tm_do, full, 0, r0, g.h, bw);
+      }
+      qdo.advance();
+    }
+    const int t_before = it.t;
+    if (!tile_next(g, it)) return;
+    new_job = it.t != t_before;
+    if (new_job) kv.advance();
+  }
+}
+
+// Tables of warpgroup w.  Pair mode: the warpgroup works on chunk w of both units, one table stage
+// per tile.  Otherwise: the existing chunks of step w of every tile, in order.
+__device__ void bwd_load_tables(const BwdParams& p, uint32_t smem_base, uint32_t bars, const WaitCtx& ctx, int w) {
+  const BwdGeom g = bwd_geom(p);
+  if (g.njobs == 0 || !(p.has_bias || p.has_mask)) return;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const uint32_t NBM = p.n_bm_stages;
+  // two boxes of 64 keys per table; in pair mode the units share the bias box (same head) and
+  // have a mask box each
+  const int n_bias = p.has_bias ? (g.pair ? 1 : 2) : 0;
+  const uint32_t tx_bytes = static_cast<uint32_t>(n_bias + (p.has_mask ? 2 : 0)) * kBoxBytes;
+  TileIt it{0, 0, 0};
+  Ring bm(NBM);
+#pragma unroll 1
+  do {
+    const int nchunks = g.pair ? 1 : min(2, (step_rows(g, it.i, w) + kChunkCols - 1) / kChunkCols);
+#pragma unroll 1
+    for (int c = 0; c < nchunks; ++c) {
+      const uint32_t st = bm.stage;
+      if (!mbar_wait(bar(kbBmFree + 2 * w + st), bm.phase ^ 1u, ctx, 72)) return;
       const uint32_t base = smem_base + p.off_bm + (w * NBM + st) * (2u * kTableTileBytes);
       const uint32_t full = bar(kbBmFull + 2 * w + st);
-      if (g.pair) {
-        // only the keys of unit w are looked at by warpgroup w
-        mbar_arrive_expect_tx(full, ntab * kBoxBytes);
-        const int bw = bwd_bw(p, g, b.it.t, w);
-        const int c0 = b.c * kChunkCols;
-        if (p.has_bias) tma_load_3d(base + w * kBoxBytes, &p.tm_biasT, full, c0, 0, g.h);
-        if (p.has_mask)
-          tma_load_3d(base + kTableTileBytes + w * kBoxBytes, &p.tm_maskT, full, c0, 0,
+      mbar_arrive_expect_tx(full, tx_bytes);
+      const int c0 = g.pair ? w * kChunkCols : it.i * kTileRows + w * kStepCols + c * kChunkCols;
+#pragma unroll 1
+      for (int hb = 0; hb < 2; ++hb) {
+        const int r0 = g.pair ? 0 : it.j * kTileRows + hb * kBoxRows;
+        if (hb < n_bias) tma_load_3d(base + hb * kBoxBytes, &p.tm_biasT, full, c0, r0, g.h);
+        if (p.has_mask) {
+          const int bw = bwd_bw(p, g, it.t, g.pair ? hb : 0);
+          tma_load_3d(base + kTableTileBytes + hb * kBoxBytes, &p.tm_maskT, full, c0, r0,
                       bw < p.BW ? bw % p.nW : 0);
-      } else {
-        mbar_arrive_expect_tx(full, ntab * 2u * kBoxBytes);
-        const int bw = bwd_bw(p, g, b.it.t, 0);
-        const int c0 = b.it.i * kTileRows + w * kStepCols + b.c * kChunkCols;
-        for (int hb = 0; hb < 2; ++hb) {
-          const int r0 = b.it.j * kTileRows + hb * kBoxRows;
-          if (p.has_bias) tma_load_3d(base + hb * kBoxBytes, &p.tm_biasT, full, c0, r0, g.h);
-          if (p.has_mask)
-            tma_load_3d(base + kTableTileBytes + hb * kBoxBytes, &p.tm_maskT, full, c0, r0, bw % p.nW);
         }
       }
-      if (++b.stage == NBM) {
-        b.stage = 0;
-        b.phase ^= 1u;
-      }
-      ++b.c;
-      bm_seek(b, w);
-      progress = true;
+      bm.advance();
     }
-    if (progress) {
-      idle = 0;
-    } else if ((++idle & 0x3Fu) != 0) {
-      __nanosleep(20);
-    } else {
-      if (idle == 0x40u) t0 = clock64();
-      if (*ctx.abort_flag) return;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        *ctx.abort_flag = 1u;
-        if (ctx.status != nullptr) {
-          if (atomicCAS(&ctx.status->code, 0u, (70u << 8) | kStatusTimeout) == 0u) {
-            ctx.status->block = blockIdx.x;
-            ctx.status->detail = (a_qdo.stage << 16) | (bc[0].stage & 0xFFFFu);
-          }
-        }
-        return;
-      }
-    }
-  }
+  } while (tile_next(g, it));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -880,13 +906,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
   if (tid == 0) {
     ctrl_words[1] = 0u;
     for (int i = 0; i < kBwdNumBars; ++i) {
+      // jobs of a single tile: K is normalised, and dK / dV are written, by warpgroup 1 alone and
+      // dQ by warpgroup 0 alone
+      const bool single = p.pair_mode || p.N <= kTileRows;
       uint32_t count = 1u;
-      if (i >= kbKvReady && i < kbKvFree) count = 256u;
-      else if (i >= kbKvFree && i < kbQdoFull) count = 257u;
+      if (i >= kbKvReady && i < kbKvFree) count = single ? 128u : 256u;
+      else if (i >= kbKvFree && i < kbQdoFull) count = single ? 129u : 257u;
       else if (i >= kbQdoReady && i < kbQdoFree) count = 256u;
-      else if (i >= kbPtFull && i < kbBmFull) count = 128u;
+      else if (i >= kbPtFull && i < kbBmFull) count = 128u;   // four chunk barriers
       else if (i >= kbBmFree && i < kbDsFree) count = 128u;
-      else if ((i >= kbDkvFree && i < kbDqFull) || (i >= kbDqFree && i < kBwdNumBars)) count = 256u;
+      else if ((i >= kbDkvFree && i < kbDqFull) || (i >= kbDqFree && i < kBwdNumBars)) count = single ? 128u : 256u;
       mbar_init(bars + 8u * i, count);
     }
     mbar_fence_init();
@@ -907,12 +936,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
   const uint32_t tmem = tmem_slot;
   WaitCtx ctx{&ctrl_words[1], p.status};
 
+#if FWA2_TRACE
+  // per-CTA wall time, clock cycles and SM id in the producer's (otherwise unused) trace region
+  unsigned long long t_start = 0;
+  long long c_start = 0;
+  if (tid == 0 && p.trace.buf != nullptr) {
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
+    c_start = clock64();
+  }
+#endif
   float dscale_acc = 0.f;
   if (warp < 8) {
     bwd_compute_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, dscale_acc);
   } else if (lane == 0) {
     if (warp == 8) bwd_mma_role<T>(p, smem_base, bars, tmem, ctx);
-    else bwd_load_role(p, smem_base, bars, ctx);
+    else if (warp == 9) bwd_load_main(p, smem_base, bars, ctx);
+    else bwd_load_tables(p, smem_base, bars, ctx, static_cast<int>(warp) - 10);
   }
   __syncwarp();
   // deterministic CTA-wide sum of the dLogitScale contributions
@@ -929,6 +968,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
     p.dscale_partial[blockIdx.x] =
         s * load_scale<T>(p.scale, p.scale_is_tensor, static_cast<int>(blockIdx.x) % p.H);
   }
+#if FWA2_TRACE
+  if (tid == 0 && p.trace.buf != nullptr && 3 * blockIdx.x + 2 < p.trace.cap) {
+    unsigned long long t_end;
+    uint32_t smid;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    p.trace.buf[2ll * p.trace.cap + 3 * blockIdx.x] = t_start;
+    p.trace.buf[2ll * p.trace.cap + 3 * blockIdx.x + 1] = t_end;
+    p.trace.buf[2ll * p.trace.cap + 3 * blockIdx.x + 2] =
+        (smid + 1000) | (static_cast<unsigned long long>(clock64() - c_start) << 16);
+  }
+#endif
   if (ctrl_words[1]) {
     __nanosleep(20000);
     __syncthreads();

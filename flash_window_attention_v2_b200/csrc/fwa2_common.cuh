@@ -25,6 +25,11 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLn100 = 4.605170185988092f;
 
 // Optional timeline of CTA 0: each role appends (clock64 << 8 | event) words to its own region.
+// Only compiled in with -DFWA2_TRACE=1 (a development aid: the extra code costs instruction-cache
+// space that the kernels cannot spare); otherwise the trace arguments are accepted and ignored.
+#ifndef FWA2_TRACE
+#define FWA2_TRACE 0
+#endif
 struct Trace {
   unsigned long long* buf;
   int cap;
@@ -35,17 +40,21 @@ struct TraceCursor {
 };
 __device__ __forceinline__ TraceCursor trace_begin(const Trace& t, int role) {
   TraceCursor c{nullptr, 0};
+#if FWA2_TRACE
   if (t.buf != nullptr && blockIdx.x == 0) {
     c.p = t.buf + static_cast<long long>(role) * t.cap;
     c.left = t.cap;
   }
+#endif
   return c;
 }
 __device__ __forceinline__ void trace_ev(TraceCursor& c, unsigned int id) {
+#if FWA2_TRACE
   if (c.left > 0) {
     *c.p++ = (static_cast<unsigned long long>(clock64()) << 8) | id;
     --c.left;
   }
+#endif
 }
 
 struct FwdParams {
@@ -75,27 +84,31 @@ struct FwdParams {
 };
 
 // Normalise one 32-element row of a 64-byte-swizzled tile in place; returns 1 / max(|x|, 1e-12).
+// Two rolled passes over the four 16-byte pieces of the row (small code matters more than the
+// second read of 64 bytes of shared memory).
 template <typename T>
 __device__ __forceinline__ float normalise_row(uint32_t tile_base, uint32_t row) {
-  uint32_t w[4][4];
+  const uint32_t row_base = tile_base + row * 64u, sw = (row >> 1) & 3u;
   float ss = 0.f;
-#pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
-    lds128(tile_base + sw64_offset(row, ch), w[ch]);
+#pragma unroll 1
+  for (uint32_t ch = 0; ch < 4u; ++ch) {
+    uint32_t w[4];
+    lds128(row_base + ((ch ^ sw) << 4), w);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float a = Elem<T>::lo(w[ch][i]), b = Elem<T>::hi(w[ch][i]);
+      const float a = Elem<T>::lo(w[i]), b = Elem<T>::hi(w[i]);
       ss = fmaf(a, a, ss);
       ss = fmaf(b, b, ss);
     }
   }
   const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+#pragma unroll 1
+  for (uint32_t ch = 0; ch < 4u; ++ch) {
+    uint32_t w[4];
+    lds128(row_base + ((ch ^ sw) << 4), w);
 #pragma unroll
-  for (int ch = 0; ch < 4; ++ch) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      w[ch][i] = Elem<T>::pack(Elem<T>::lo(w[ch][i]) * rn, Elem<T>::hi(w[ch][i]) * rn);
-    sts128(tile_base + sw64_offset(row, ch), w[ch]);
+    for (int i = 0; i < 4; ++i) w[i] = Elem<T>::pack(Elem<T>::lo(w[i]) * rn, Elem<T>::hi(w[i]) * rn);
+    sts128(row_base + ((ch ^ sw) << 4), w);
   }
   return rn;
 }

@@ -83,28 +83,34 @@ struct WaitCtx {
 // About one second at ~1.9 GHz: far beyond any legitimate wait in these kernels.
 constexpr long long kWaitLimitCycles = 2000000000ll;
 
-// Bounded wait on an mbarrier phase.  Returns false if the wait was abandoned.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                          uint32_t site) {
-  if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait on an mbarrier phase.  Returns false if the wait was abandoned.  The polling loop
+// is kept out of line: the kernels that use it are bound by instruction fetch, and the fast path
+// (the phase has already completed) is what runs nearly every time.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                            DeviceStatus* status, uint32_t site) {
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3Fu) == 0) {
-      if (*ctx.abort_flag) return false;
+      if (*abort_flag) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
-        *ctx.abort_flag = 1u;
-        if (ctx.status != nullptr) {
-          if (atomicCAS(&ctx.status->code, 0u, (site << 8) | kStatusTimeout) == 0u) {
-            ctx.status->block = blockIdx.x;
-            ctx.status->detail = parity;
+        *abort_flag = 1u;
+        if (status != nullptr) {
+          if (atomicCAS(&status->code, 0u, (site << 8) | kStatusTimeout) == 0u) {
+            status->block = blockIdx.x;
+            status->detail = parity;
           }
         }
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                          uint32_t site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, ctx.abort_flag, ctx.status, site);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -183,6 +189,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// 32 lanes x 8 columns.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -244,6 +263,16 @@ struct Ring {
     }
   }
 };
+
+// Warpgroup-wide register reallocation (all four warps of a warpgroup execute the same one).
+template <uint32_t kRegs>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <uint32_t kRegs>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
 
 // One lane of a fully converged warp (the same lane every time).
 __device__ __forceinline__ bool elect_one() {
