@@ -15,6 +15,14 @@
 //   warps 10-11 TMA producers of the bias / mask tables of warpgroup 0 / 1 (one thread each)
 // Replaces flash_win_attn_v2/kernels/attn_kernel_backward.py:6-51 (delta pre-pass) and
 // :84-564 (`_bwd_kernel`).
+#ifndef FWA2_BWD_NORMALISE_ROLLED
+#define FWA2_BWD_NORMALISE_ROLLED 1
+#endif
+#ifndef FWA2_BWD_WAIT_INLINE
+#define FWA2_BWD_WAIT_INLINE 0
+#endif
+#define FWA2_NORMALISE_ROLLED FWA2_BWD_NORMALISE_ROLLED
+#define FWA2_WAIT_INLINE FWA2_BWD_WAIT_INLINE
 #include "fwa2_common.cuh"
 
 namespace fwa2 {

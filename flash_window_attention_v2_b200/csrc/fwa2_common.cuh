@@ -83,6 +83,10 @@ struct FwdParams {
   Trace trace;
 };
 
+#ifndef FWA2_NORMALISE_ROLLED
+#define FWA2_NORMALISE_ROLLED 1
+#endif
+#if FWA2_NORMALISE_ROLLED
 // Normalise one 32-element row of a 64-byte-swizzled tile in place; returns 1 / max(|x|, 1e-12).
 // Two rolled passes over the four 16-byte pieces of the row (small code matters more than the
 // second read of 64 bytes of shared memory).
@@ -113,6 +117,34 @@ __device__ __forceinline__ float normalise_row(uint32_t tile_base, uint32_t row)
   return rn;
 }
 
+#else
+// Normalise one 32-element row of a 64-byte-swizzled tile in place; returns 1 / max(|x|, 1e-12).
+template <typename T>
+__device__ __forceinline__ float normalise_row(uint32_t tile_base, uint32_t row) {
+  uint32_t w[4][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    lds128(tile_base + sw64_offset(row, ch), w[ch]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = Elem<T>::lo(w[ch][i]), b = Elem<T>::hi(w[ch][i]);
+      ss = fmaf(a, a, ss);
+      ss = fmaf(b, b, ss);
+    }
+  }
+  const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      w[ch][i] = Elem<T>::pack(Elem<T>::lo(w[ch][i]) * rn, Elem<T>::hi(w[ch][i]) * rn);
+    sts128(tile_base + sw64_offset(row, ch), w[ch]);
+  }
+  return rn;
+}
+
+#endif
 // Multiplier of the cosine scores: exp(min(g_h, ln 100)) in tensor mode, the given fp32 constant
 // in scalar mode.
 template <typename T>

@@ -7,6 +7,17 @@
 //   warp  4    issues every tcgen05.mma (one thread)
 //   warp  5    TMA producer (one thread): K, V, Q tiles and the bias / mask table chunks
 // Replaces flash_win_attn_v2/kernels/attn_kernel_forward.py:21-258 (`_fwd_kernel`).
+#ifndef FWA2_FWD_ROLLED_STEP
+#define FWA2_FWD_ROLLED_STEP 0
+#endif
+#ifndef FWA2_FWD_NORMALISE_ROLLED
+#define FWA2_FWD_NORMALISE_ROLLED 0
+#endif
+#ifndef FWA2_FWD_WAIT_INLINE
+#define FWA2_FWD_WAIT_INLINE 1
+#endif
+#define FWA2_NORMALISE_ROLLED FWA2_FWD_NORMALISE_ROLLED
+#define FWA2_WAIT_INLINE FWA2_FWD_WAIT_INLINE
 #include "fwa2_common.cuh"
 
 namespace fwa2 {
@@ -129,6 +140,145 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
 #pragma unroll
       for (int i = 0; i < 32; ++i) acc[i] = 0.f;
 
+#if FWA2_FWD_ROLLED_STEP
+      for (int s = 0; s < sh.KS; ++s, s_ring.advance()) {
+        const int ncols = sh.pair ? sh.N : min(kStepCols, sh.N - s * kStepCols);
+        const int nch = ncols > kChunkCols ? 2 : 1;
+        const uint32_t sb = s_ring.stage;
+        if (!mbar_wait(bar(kBarSFull + sb), s_ring.phase, ctx, 12)) return;
+        tc_fence_after();
+        trace_ev(tr, 10);
+        const uint32_t t_s = tmem + lane_base + kTmemS + (sh.pair ? hf * 64u : sb * 64u);
+
+        // Both passes over the 64 scores of the row run as rolled loops over groups of eight
+        // columns (this kernel is bound by instruction fetch: the loop bodies have to stay in the
+        // instruction cache), two groups per trip so that the tensor-memory load of one group
+        // overlaps the arithmetic of the other.
+        // ---- pass 1: x = scale * cos + bias + mask, written back over the scores; row maximum ----
+        float mxp[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        {
+          const uint32_t row_off = tid * 64u, row_sw = (tid >> 1) & 3u;
+          uint32_t bm_base = 0;
+          auto group1 = [&](uint32_t g8, uint32_t (&r)[8]) {
+            // g8: group index 0..7; r: its eight scores, replaced by x
+            const int col0 = static_cast<int>(g8) * 8;
+            const bool live = any_table && static_cast<int>(g8 >> 2) < nch;
+            uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
+            if (live) {
+              const uint32_t off = row_off + (((g8 & 3u) ^ row_sw) << 4);
+              if (p.has_bias) lds128(bm_base + off, wb);
+              if (p.has_mask) lds128(bm_base + kTableTileBytes + off, wm);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float x0 = fmaf(__uint_as_float(r[2 * i]), scale, Elem<T>::lo(wb[i])) + Elem<T>::lo(wm[i]);
+              float x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale, Elem<T>::hi(wb[i])) + Elem<T>::hi(wm[i]);
+              if (col0 + 8 > ncols) {   // columns past the end of the window
+                if (col0 + 2 * i >= ncols) x0 = -INFINITY;
+                if (col0 + 2 * i + 1 >= ncols) x1 = -INFINITY;
+              }
+              mxp[i] = fmaxf(mxp[i], fmaxf(x0, x1));
+              r[2 * i] = __float_as_uint(x0);
+              r[2 * i + 1] = __float_as_uint(x1);
+            }
+          };
+          uint32_t ra[8], rb[8];
+          tmem_ld8(t_s, ra);
+#pragma unroll 1
+          for (uint32_t g8 = 0; g8 < 8u; g8 += 2u) {
+            if ((g8 & 3u) == 0u && any_table && static_cast<int>(g8 >> 2) < nch) {
+              const uint32_t st = bm_ring.stage;
+              bm_base = smem_base + p.off_bm + st * (2u * kTableTileBytes);
+              if (!mbar_wait(bar(kBarBmFull + st), bm_ring.phase, ctx, 13)) return;
+            }
+            tmem_wait_ld();
+            tmem_ld8(t_s + 8u * (g8 + 1u), rb);
+            group1(g8, ra);
+            tmem_st8(t_s + 8u * g8, ra);
+            tmem_wait_ld();
+            if (g8 + 2u < 8u) tmem_ld8(t_s + 8u * (g8 + 2u), ra);
+            group1(g8 + 1u, rb);
+            tmem_st8(t_s + 8u * (g8 + 1u), rb);
+            if ((g8 & 3u) == 2u && any_table && static_cast<int>(g8 >> 2) < nch) {
+              mbar_arrive(bar(kBarBmFree + bm_ring.stage));
+              bm_ring.advance();
+            }
+          }
+        }
+        trace_ev(tr, 12);
+        // ---- online softmax ----
+        const float mx = fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3]));
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = ex2f((m_run - m_use) * kLog2e);
+        const float ml2 = m_use * kLog2e;
+        trace_ev(tr, 13);
+        // ---- fold the previous step's P*V into the running output (this also makes sure that the
+        // tensor core has finished reading the previous P before pass 2 overwrites it) ----
+        if (s > 0) {
+          if (!mbar_wait(bar(kBarPvDone), pvc & 1u, ctx, 14)) return;
+          ++pvc;
+          tc_fence_after();
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_base + kTmemPV, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha_pend, __uint_as_float(r[i]));
+        }
+        alpha_pend = alpha;
+        trace_ev(tr, 14);
+
+        tmem_wait_st();
+        // ---- pass 2: p = exp(x - max), row sum, P handed to the tensor core in 16-bit pairs ----
+        float sp[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          const uint32_t t_p = tmem + lane_base + kTmemP + (sh.pair ? hf * 32u : 0u);
+          const uint32_t p_row = smem_base + p.off_p + (sh.pair ? hf * 16384u : 0u) + tid * 128u, p_sw = tid & 7u;
+          auto group2 = [&](uint32_t g8, const uint32_t (&r)[8]) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float p0 = ex2f(fmaf(__uint_as_float(r[2 * i]), kLog2e, -ml2));
+              const float p1 = ex2f(fmaf(__uint_as_float(r[2 * i + 1]), kLog2e, -ml2));
+              sp[i] += p0 + p1;
+              w[i] = Elem<T>::pack(p0, p1);
+            }
+            if constexpr (kPTmem) tmem_st4(t_p + 4u * g8, w);
+            else sts128(p_row + ((g8 ^ p_sw) << 4), w);
+          };
+          uint32_t ra[8], rb[8];
+          tmem_ld8(t_s, ra);
+#pragma unroll 1
+          for (uint32_t g8 = 0; g8 < 8u; g8 += 2u) {
+            tmem_wait_ld();
+            tmem_ld8(t_s + 8u * (g8 + 1u), rb);
+            group2(g8, ra);
+            tmem_wait_ld();
+            if (g8 + 2u < 8u) tmem_ld8(t_s + 8u * (g8 + 2u), ra);
+            group2(g8 + 1u, rb);
+          }
+        }
+        // the scores are no longer needed: the tensor core may overwrite them
+        tc_fence_before();
+        mbar_arrive(bar(kBarSFree + sb));
+        trace_ev(tr, 11);
+        const float sum = (sp[0] + sp[1]) + (sp[2] + sp[3]);
+        l_run = fmaf(l_run, alpha, sum);
+        m_run = m_new;
+
+        // ---- hand P to the tensor core ----
+        if constexpr (kPTmem) {
+          tmem_wait_st();
+          tc_fence_before();
+        } else {
+          fence_proxy_async_smem();
+          tc_fence_before();
+        }
+        mbar_arrive(bar(kBarPFull));
+        trace_ev(tr, 15);
+      }
+
+#else
       for (int s = 0; s < sh.KS; ++s, s_ring.advance()) {
         const int ncols = sh.pair ? sh.N : min(kStepCols, sh.N - s * kStepCols);
         // ---- scores of this step out of tensor memory ----
@@ -260,6 +410,7 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
         trace_ev(tr, 15);
       }
 
+#endif
       // ---- prologue of the next tile (and job) ----
       if (mt + 1 < sh.MT) {
         if (!prologue_q(tt + 1)) return;
@@ -370,11 +521,11 @@ __device__ void fwd_mma_role(const FwdParams& p, uint32_t smem_base, uint32_t ba
         trace_ev(tr, 33);
         const uint32_t vb = sh.pair ? v_base : v_base + static_cast<uint32_t>(s) * (kStepCols * kRowBytes);
         if constexpr (kPTmem) {
-#pragma unroll 4
+#pragma unroll 1
           for (uint32_t k = 0; k < pv_ksteps; ++k)
             mma_ts(tmem + kTmemPV, tmem + kTmemP + k * 8u, desc_at(dv64, vb + k * 1024u), idesc_pv, k);
         } else {
-#pragma unroll 4
+#pragma unroll 1
           for (uint32_t k = 0; k < pv_ksteps; ++k)
             mma_ss(tmem + kTmemPV, desc_at(dp128, (k >> 2) * 16384u + (k & 3u) * 32u),
                    desc_at(dv64, vb + k * 1024u), idesc_pv, k);
@@ -424,6 +575,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
   long long t0 = clock64();
   uint32_t idle = 0;
   TraceCursor tr = trace_begin(p.trace, 2);
+#pragma unroll 1
   while (!a_done || !b_done) {
     bool progress = false;
     if (!a_done) {
@@ -435,6 +587,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
           const uint32_t full = bar(kBarKvFull + kvs);
           mbar_arrive_expect_tx(full, 2u * static_cast<uint32_t>(sh.rows_kv) * kRowBytes);
           const int nbox = sh.rows_kv / kBoxRows;
+#pragma unroll 1
           for (int b = 0; b < nbox; ++b) {
             const int ui = sh.pair ? b : 0;
             const int r0 = sh.pair ? 0 : b * kBoxRows;
@@ -452,6 +605,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
           const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
           const uint32_t qfull = bar(kBarQFull + qs);
           mbar_arrive_expect_tx(qfull, 2u * kBoxBytes);
+#pragma unroll 1
           for (int b = 0; b < 2; ++b) {
             const int ui = sh.pair ? b : 0;
             const int r0 = sh.pair ? 0 : mt * kTileRows + b * kBoxRows;
@@ -476,6 +630,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
         const uint32_t base = smem_base + p.off_bm + st * (2u * kTableTileBytes);
         const uint32_t full = bar(kBarBmFull + st);
         mbar_arrive_expect_tx(full, table_bytes);
+#pragma unroll 1
         for (int b = 0; b < 2; ++b) {
           const int ui = sh.pair ? b : 0;
           const int r0 = sh.pair ? 0 : b_mt * kTileRows + b * kBoxRows;

@@ -107,10 +107,34 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     }
   }
 }
+#ifndef FWA2_WAIT_INLINE
+#define FWA2_WAIT_INLINE 0
+#endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           uint32_t site) {
   if (mbar_try_wait(bar, parity)) return true;
+#if FWA2_WAIT_INLINE
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0x3Fu) == 0) {
+      if (*ctx.abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *ctx.abort_flag = 1u;
+        if (ctx.status != nullptr) {
+          if (atomicCAS(&ctx.status->code, 0u, (site << 8) | kStatusTimeout) == 0u) {
+            ctx.status->block = blockIdx.x;
+            ctx.status->detail = parity;
+          }
+        }
+        return false;
+      }
+    }
+  }
+#else
   return mbar_wait_slow(bar, parity, ctx.abort_flag, ctx.status, site);
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -195,6 +219,11 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
                  "=r"(r[7])
                : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                : "memory");
 }
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t (&r)[4]) {
