@@ -365,7 +365,7 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   const bool any_table = has_bias || has_mask;
   auto total = [&](uint32_t nkv, uint32_t nds, uint32_t nbm) {
     return nkv * p.kv_stage_bytes + qdo_bytes + nds * 32768u + (any_table ? 2u * nbm * bm_stage : 0u) +
-           nkv * static_cast<uint32_t>(p.rows_kv) * 4u + 3u * 1024u + kCtrlBytes;
+           2048u + nkv * static_cast<uint32_t>(p.rows_kv) * 4u + 3u * 1024u + kCtrlBytes;
   };
   const uint32_t budget = static_cast<uint32_t>(dev.max_smem_optin);
   // preference order; a job of one tile (at most 128 keys) wants three K/V stages, see
@@ -373,11 +373,13 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   // Jobs of a single tile (windows of at most 128 tokens) release their K/V stage only in the
   // epilogue that runs one tile late, so they want four stages to keep a whole tile of lead for
   // the next load.
-  const uint32_t opts[][3] = {{4, 2, 2}, {4, 1, 2}, {3, 2, 2}, {3, 1, 2}, {2, 2, 2}, {2, 1, 2},
+  const uint32_t opts[][3] = {{4, 2, 2}, {4, 2, 1}, {4, 1, 2}, {3, 2, 2}, {3, 1, 2}, {2, 2, 2}, {2, 1, 2},
                               {1, 2, 2}, {1, 1, 2}, {1, 1, 1}};
   uint32_t nkv = 0, nds = 0, nbm = 0;
   for (const auto& o : opts) {
     if (o[0] >= 3 && p.rows_kv > 128) continue;
+    // one table stage per warpgroup is enough only in pair mode (one chunk per tile and warpgroup)
+    if (o[0] == 4 && o[2] == 1 && !pl.pair) continue;
     if (total(o[0], o[1], o[2]) <= budget) { nkv = o[0]; nds = o[1]; nbm = o[2]; break; }
   }
   if (nkv == 0) return FWA2_ERR_SHAPE;
@@ -388,7 +390,8 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   p.off_qdo = p.off_kv + nkv * p.kv_stage_bytes;
   p.off_ds = p.off_qdo + qdo_bytes;
   p.off_bm = p.off_ds + nds * 32768u;
-  p.off_rk = p.off_bm + (any_table ? 2u * nbm * bm_stage : 0u);
+  p.off_ident = p.off_bm + (any_table ? 2u * nbm * bm_stage : 0u);
+  p.off_rk = p.off_ident + 2048u;
   p.off_rowstats = p.off_rk + nkv * static_cast<uint32_t>(p.rows_kv) * 4u;
   p.off_ctrl = p.off_rowstats + 3u * 1024u;
   p.smem_bytes = p.off_ctrl + kCtrlBytes;

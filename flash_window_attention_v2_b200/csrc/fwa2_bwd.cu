@@ -41,6 +41,10 @@ __device__ __forceinline__ uint32_t tm_dk(uint32_t set) { return 288u + 64u * se
 __device__ __forceinline__ uint32_t tm_dq(uint32_t nsets, uint32_t set, uint32_t i) {
   return (nsets == 2u ? 384u + 64u * set : 320u) + 32u * i;
 }
+// Pair mode keeps the window-summed dBias^T of the CTA's head in tensor memory for the whole
+// kernel: lanes = keys of unit A | unit B, 32 query columns per chunk, in the columns that the
+// second dQ accumulator of a set would use (windows of at most 64 tokens have one query tile).
+__device__ __forceinline__ uint32_t tm_db(uint32_t chunk) { return 416u + 64u * chunk; }
 constexpr uint32_t kQdoStageBytes = 4u * kBoxBytes;   // [Q tile | dO tile]
 constexpr uint32_t kDsTileBytes = 32768u;
 constexpr int kNumQdoStages = 3;
@@ -350,34 +354,44 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     return true;
   };
   // ---- dQ of a job (thread = query): warpgroup (i mod 2) writes query tile i ----
+  // dq = scale * (dQ' - q^ (q^ . dQ')) / |q| from the raw q row: with q^ = q / |q| the dot product
+  // is (q . dQ') / |q|, so one pass gives |q| and the dot product, a second the output.  The raw
+  // row is fetched with four loads in flight before anything is waited for; every lane runs both
+  // passes (the tensor-memory loads are warp-wide), only the global accesses are predicated.
   auto dq_epilogue = [&](int t_e, uint32_t kq) -> bool {
     if (single_tile && wg == 1) return true;
+    const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
+    const int bwq = bwd_bw(p, g, t_e, mq);
+    uint4 qraw[4];
+    auto load_q = [&](int i) -> bool {
+      const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
+      const bool okq = bwq < p.BW && ig < g.N;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) qraw[ch] = make_uint4(0u, 0u, 0u, 0u);
+      if (okq) {
+        const uint16_t* qrow = static_cast<const uint16_t*>(p.q) + bwq * p.q_sbw + g.h * p.q_sh + ig * p.q_sn;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) qraw[ch] = ldg_nc_v4(qrow + ch * 8);
+      }
+      return okq;
+    };
+    bool okq = load_q(static_cast<int>(wg));
     // dQ of every query tile of the job is complete
     const uint32_t set = kq & sets_mask, use = kq >> sets_shift;
     if (!mbar_wait(bar(kbDqFull + set), use & 1u, ctx, 56)) return false;
     tc_fence_after();
     trace_ev(tr, 12);
-    const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
-    const int bwq = bwd_bw(p, g, t_e, mq);
 #pragma unroll 1
     for (int i = static_cast<int>(wg); i < g.MT; i += 2) {
       const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
-      const bool okq = bwq < p.BW && ig < g.N;
       const uint32_t t_dq = tmem + lane_base + tm_dq(nsets, set, static_cast<uint32_t>(i));
-      // dq = scale * (dQ' - q^ (q^ . dQ')) / |q| from the raw q row: with q^ = q / |q| the dot
-      // product is (q . dQ') / |q|, so one pass gives |q| and the dot product, a second the output.
-      // Every lane runs both loops (the tensor-memory loads are warp-wide); only the global
-      // accesses are predicated.
-      const uint16_t* qrow = static_cast<const uint16_t*>(p.q) + bwq * p.q_sbw + g.h * p.q_sh + ig * p.q_sn;
       float ss = 0.f, qd = 0.f;
-#pragma unroll 1
-      for (uint32_t gq = 0; gq < 4u; ++gq) {
+#pragma unroll
+      for (int gq = 0; gq < 4; ++gq) {
         uint32_t r[8];
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (okq) v = ldg_nc_v4(qrow + 8u * gq);
         tmem_ld8(t_dq + 8u * gq, r);
         tmem_wait_ld();
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t w[4] = {qraw[gq].x, qraw[gq].y, qraw[gq].z, qraw[gq].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float a = Elem<T>::lo(w[e]), b = Elem<T>::hi(w[e]);
@@ -392,14 +406,12 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       if (okq) dscale_acc += dot;
       const float f = scale * rn, cq = rn * dot;
       uint16_t* dst = static_cast<uint16_t*>(p.dq) + bwq * p.dq_sbw + g.h * p.dq_sh + ig * p.dq_sn;
-#pragma unroll 1
-      for (uint32_t gq = 0; gq < 4u; ++gq) {
+#pragma unroll
+      for (int gq = 0; gq < 4; ++gq) {
         uint32_t r[8];
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (okq) v = ldg_nc_v4(qrow + 8u * gq);
         tmem_ld8(t_dq + 8u * gq, r);
         tmem_wait_ld();
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t w[4] = {qraw[gq].x, qraw[gq].y, qraw[gq].z, qraw[gq].w};
         float o8[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -411,8 +423,9 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
         o.y = Elem<T>::pack(o8[2], o8[3]);
         o.z = Elem<T>::pack(o8[4], o8[5]);
         o.w = Elem<T>::pack(o8[6], o8[7]);
-        if (okq) *reinterpret_cast<uint4*>(dst + 8u * gq) = o;
+        if (okq) *reinterpret_cast<uint4*>(dst + 8 * gq) = o;
       }
+      if (i + 2 < g.MT) okq = load_q(i + 2);
     }
     tc_fence_before();
     mbar_arrive(bar(kbDqFree + set));
@@ -489,7 +502,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       const float* delta = rowstats + qs * 256u + 128u + step * 64u;
       const long long db_buf = g.pair ? 2ll * blockIdx.x + um : static_cast<long long>(blockIdx.x);
       const int ig0 = g.pair ? 0 : cur.i * kTileRows + static_cast<int>(wg) * kStepCols;
-      float* db_row = (p.db_partial != nullptr && key_ok)
+      float* db_row = (p.db_partial != nullptr && key_ok && !g.pair)   // pair mode: summed by the tensor core
                           ? p.db_partial + db_buf * p.db_buf_stride + static_cast<long long>(jg) * p.db_pitch + ig0
                           : nullptr;
       const bool db_store = (jt == 0);
@@ -591,40 +604,30 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     // ------------------------------ epilogues ------------------------------
     // With two accumulator sets they run one tile late: by then the products they read have
     // long been finished, and the tensor core is not left waiting for this warpgroup either.
-    if (pend_dkv) {
-      if (!dkv_epilogue(pd_it, pd_kvs, pd_k)) return;
-      pend_dkv = false;
-    }
-    if (pend_dq) {
-      if (!dq_epilogue(pq_t, pq_k)) return;
-      pend_dq = false;
-    }
-    if (cur.i == g.MT - 1) {
-      if (nsets == 2u) {
-        pend_dkv = true; pd_it = cur; pd_kvs = kvs; pd_k = kdkv;
-      } else {
-        if (!dkv_epilogue(cur, kvs, kdkv)) return;
+    // Pass 0 runs what the previous tile deferred, pass 1 this tile's own epilogues when they
+    // cannot be deferred (one accumulator set, or no further tile); one loop, so that the code
+    // of the epilogues exists once.
+    const bool last_q = cur.i == g.MT - 1, last_k = last_q && cur.j == g.KB - 1;
+    const bool defer = nsets == 2u && has_next;
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+      const bool run_dkv = pass == 0 ? pend_dkv : (last_q && !defer);
+      const bool run_dq = pass == 0 ? pend_dq : (last_k && !defer);
+      if (run_dkv) {
+        if (!dkv_epilogue(pass == 0 ? pd_it : cur, pass == 0 ? pd_kvs : kvs, pass == 0 ? pd_k : kdkv)) return;
       }
-      ++kdkv;
-      if (cur.j == g.KB - 1) {
-        if (nsets == 2u) {
-          pend_dq = true; pq_t = cur.t; pq_k = kdq;
-        } else {
-          if (!dq_epilogue(cur.t, kdq)) return;
-        }
-        ++kdq;
+      if (run_dq) {
+        if (!dq_epilogue(pass == 0 ? pq_t : cur.t, pass == 0 ? pq_k : kdq)) return;
       }
     }
+    pend_dkv = last_q && defer;
+    pend_dq = last_k && defer;
+    if (pend_dkv) { pd_it = cur; pd_kvs = kvs; pd_k = kdkv; }
+    if (pend_dq) { pq_t = cur.t; pq_k = kdq; }
+    if (last_q) ++kdkv;
+    if (last_k) ++kdq;
 
-    if (!has_next) {
-      if (pend_dkv) {
-        if (!dkv_epilogue(pd_it, pd_kvs, pd_k)) return;
-      }
-      if (pend_dq) {
-        if (!dq_epilogue(pq_t, pq_k)) return;
-      }
-      break;
-    }
+    if (!has_next) break;
     if (defer_job) {
       if (!prologue_job(kv_next)) return;
     }
@@ -635,6 +638,29 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     qdo_ring = qdo_next;
     ds_ring.advance();
     cur = nxt;
+  }
+
+  // Pair mode: the dBias^T sums of this CTA leave tensor memory once, here.  Every product that
+  // fed them was issued before the commits the last epilogues waited for.  Warpgroup w writes
+  // the queries of chunk w; the buffer of unit slot m holds the keys on lanes [64 m, 64 m + 64).
+  if (g.pair && p.db_partial != nullptr) {
+    tc_fence_after();
+    const int jg = static_cast<int>(lt & 63u);
+    float* dst = p.db_partial + (2ll * blockIdx.x + (lt >> 6)) * p.db_buf_stride +
+                 static_cast<long long>(jg) * p.db_pitch + kChunkCols * wg;
+    const bool row_ok = jg < g.N && static_cast<int>(kChunkCols * wg) < p.db_pitch;
+    const uint32_t t_db = tmem + lane_base + tm_db(wg);
+#pragma unroll 1
+    for (uint32_t gq = 0; gq < 4u; ++gq) {
+      uint32_t r[8];
+      tmem_ld8(t_db + 8u * gq, r);
+      tmem_wait_ld();
+      if (row_ok) {
+        *reinterpret_cast<uint4*>(dst + 8u * gq) = make_uint4(r[0], r[1], r[2], r[3]);
+        *reinterpret_cast<uint4*>(dst + 8u * gq + 4) = make_uint4(r[4], r[5], r[6], r[7]);
+      }
+    }
+    tc_fence_before();
   }
 }
 
@@ -667,21 +693,25 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
     b.dO = b.q + 2u * kBoxBytes;
     return b;
   };
-  // S^T = K^ Q^^T and dP^T = V dO^T for the 32-query chunk c of step w of a tile.  All 32 columns
-  // are always computed: query rows past the end of the window are zeros in shared memory.
-  const uint32_t idesc_s = make_idesc(fmt, 128, kChunkCols, 0, 0);
-  auto issue_sdp = [&](const TileIt& it, int w, int c, const Bases& b) {
+  // S^T = K^ Q^^T and dP^T = V dO^T for the 64 queries of step w of a tile (two chunks; each chunk
+  // that exists has its own barrier).  All 64 columns are always computed: query rows past the end
+  // of the window are zeros in shared memory.
+  const uint32_t idesc_s = make_idesc(fmt, 128, kStepCols, 0, 0);
+  auto chunk_exists = [&](const TileIt& it, int w, int c) { return step_rows(g, it.i, w) - kChunkCols * c > 0; };
+  auto issue_sdp = [&](const TileIt& it, int w, const Bases& b) {
+    if (!chunk_exists(it, w, 0)) return;
     const uint32_t key_off = g.pair ? 0u : static_cast<uint32_t>(it.j) * (kTileRows * kRowBytes);
-    const uint32_t row_off = static_cast<uint32_t>(w * kStepCols + c * kChunkCols) * kRowBytes;
-    const uint32_t st = tmem + w * 128u + kTmST + 32u * c, dpt = tmem + w * 128u + kTmDPT + 32u * c;
+    const uint32_t row_off = static_cast<uint32_t>(w * kStepCols) * kRowBytes;
+    const uint32_t st = tmem + w * 128u + kTmST, dpt = tmem + w * 128u + kTmDPT;
     // the two accumulation chains are interleaved: back-to-back MMAs into one accumulator wait
     // for each other
-#pragma unroll 1
+#pragma unroll
     for (uint32_t k = 0; k < 2u; ++k) {
       mma_ss(st, desc_at(dk64, b.k + key_off + 32u * k), desc_at(dk64, b.q + row_off + 32u * k), idesc_s, k);
       mma_ss(dpt, desc_at(dk64, b.v + key_off + 32u * k), desc_at(dk64, b.dO + row_off + 32u * k), idesc_s, k);
     }
-    mma_commit(bar(kbStFull + 2 * w + c));
+    mma_commit(bar(kbStFull + 2 * w));
+    if (chunk_exists(it, w, 1)) mma_commit(bar(kbStFull + 2 * w + 1));
   };
 
   uint32_t kdkv = 0, kdq = 0;
@@ -689,19 +719,18 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
   const uint32_t sets_mask = nsets - 1u, sets_shift = nsets - 1u;
   TraceCursor tr = trace_begin(p.trace, 1);
   uint32_t nst = 0u;   // phase bit per (2 * warpgroup + chunk)
+  const bool db_in_tmem = g.pair && p.db_partial != nullptr;
+  const uint32_t ident = smem_base + p.off_ident;
+  uint32_t db_started[2] = {0u, 0u};
   Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS);
   TileIt cur{0, 0, 0};
-  auto chunk_exists = [&](const TileIt& it, int w, int c) { return step_rows(g, it.i, w) - kChunkCols * c > 0; };
   if (!mbar_wait(bar(kbKvReady + 0), 0u, ctx, 60)) return;
   if (!mbar_wait(bar(kbQdoReady + 0), 0u, ctx, 61)) return;
   tc_fence_after();
   {
     const Bases b0 = stage_bases(kv_ring, qdo_ring);
 #pragma unroll 1
-    for (int c = 0; c < 2; ++c)
-#pragma unroll 1
-      for (int w = 0; w < 2; ++w)
-        if (chunk_exists(cur, w, c)) issue_sdp(cur, w, c, b0);
+    for (int w = 0; w < 2; ++w) issue_sdp(cur, w, b0);
   }
 
   while (true) {
@@ -739,15 +768,24 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
           const uint32_t row_off = static_cast<uint32_t>(w * kStepCols + c * kChunkCols) * kRowBytes;
           const uint32_t first = (cur.i > 0 || w > 0 || c > 0) ? 1u : 0u;
           const uint32_t a_p = tmem + w * 128u + kTmST + 32u * c, a_ds = tmem + w * 128u + kTmDPT + 32u * c;
-#pragma unroll 1
+#pragma unroll
           for (uint32_t k = 0; k < 2; ++k) {
             mma_ts(tmem + tm_dv(kdkv & sets_mask), a_p + k * 8u, desc_at(dm64, b.dO + row_off + k * 1024u),
                    idesc_acc, first | k);
             mma_ts(tmem + tm_dk(kdkv & sets_mask), a_ds + k * 8u, desc_at(dm64, b.q + row_off + k * 1024u),
                    idesc_acc, first | k);
           }
+          if (db_in_tmem) {
+            // dBias^T += dS^T * I: the tensor core sums over the windows of this CTA
+#pragma unroll
+            for (uint32_t k = 0; k < 2; ++k)
+              mma_ts(tmem + tm_db(static_cast<uint32_t>(c)), a_ds + k * 8u, desc_at(dm64, ident + k * 1024u), idesc_acc,
+                     db_started[c] | k);
+            db_started[c] = 1u;
+          }
         }
-        if (look_now) {
+        // the next tile's scores of step w go over this tile's P^T / dS^T of both chunks
+        if (look_now && c == 1) {
           if (!looked) {
             if (cross) {
               if (!mbar_wait(bar(kbKvReady + kv_next.stage), kv_next.phase, ctx, 65)) return;
@@ -756,7 +794,7 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
             tc_fence_after();
             looked = true;
           }
-          if (chunk_exists(nxt, w, c)) issue_sdp(nxt, w, c, bn);
+          issue_sdp(nxt, w, bn);
           trace_ev(tr, 34 + w);
         }
       }
@@ -789,10 +827,7 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
       if (!mbar_wait(bar(kbQdoReady + qdo_next.stage), qdo_next.phase, ctx, 68)) return;
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c)
-#pragma unroll 1
-        for (int w = 0; w < 2; ++w)
-          if (chunk_exists(nxt, w, c)) issue_sdp(nxt, w, c, bn);
+      for (int w = 0; w < 2; ++w) issue_sdp(nxt, w, bn);
     }
     kv_ring = kv_next;
     qdo_ring = qdo_next;
@@ -938,6 +973,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
     tmem_alloc(smem_u32(&tmem_slot), kBwdTmemCols);
     tmem_relinquish();
   }
+  // 32 x 32 identity in the layout of a dO chunk (row = query, 64 bytes of columns, 16-byte pieces
+  // XOR-swizzled with the row): B operand of the products that sum dS^T into dBias^T
+  for (uint32_t wi = tid; wi < 512u; wi += kBwdThreads) {
+    const uint32_t row = wi >> 4, piece = (wi >> 2) & 3u, word = wi & 3u;   // word = two columns
+    const uint32_t col = ((piece ^ ((row >> 1) & 3u)) << 3) + 2u * word;     // logical column of the low half
+    const uint32_t one = Elem<T>::pack(1.f, 0.f) & 0xFFFFu;
+    uint32_t v = 0u;
+    if (col == row) v = one;
+    if (col + 1u == row) v = one << 16;
+    reinterpret_cast<uint32_t*>(smem_raw + p.off_ident)[wi] = v;
+  }
+  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
