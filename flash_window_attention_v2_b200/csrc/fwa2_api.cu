@@ -65,7 +65,7 @@ DeviceInfo device_info() {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // (BW, H, N, 32) tensor of 16-bit elements -> 4-D map (d, N, H, BW), box (32, 64, 1, 1).
-int encode_rows4(CUtensorMap* m, const fwa2_tensor4& t, int dtype, int bw, int h, int n) {
+int encode_rows4(CUtensorMap* m, const fwa2_tensor4& t, int dtype, int bw, int h, int n, int box_rows = kBoxRows) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return FWA2_ERR_DRIVER;
   if (t.ptr == nullptr) return FWA2_ERR_NULL;
@@ -83,7 +83,7 @@ int encode_rows4(CUtensorMap* m, const fwa2_tensor4& t, int dtype, int bw, int h
     const int64_t se = (ext[i] > 1) ? s[i] : static_cast<int64_t>(kHeadDim);
     strides[i] = static_cast<cuuint64_t>(se) * 2u;
   }
-  cuuint32_t box[4] = {static_cast<cuuint32_t>(kHeadDim), static_cast<cuuint32_t>(kBoxRows), 1u, 1u};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(kHeadDim), static_cast<cuuint32_t>(box_rows), 1u, 1u};
   cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
   CUresult r = enc(m, dtype == FWA2_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                    4, t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -326,10 +326,13 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
 
   BwdParams p;
   std::memset(&p, 0, sizeof(p));
-  if ((rc = encode_rows4(&p.tm_q, a->q, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+  // pair mode loads Q and dO in boxes of 32 rows, so that the queries of the two units can be
+  // interleaved in shared memory (see the kernel)
+  const int q_box_rows = pl.pair ? 32 : kBoxRows;
+  if ((rc = encode_rows4(&p.tm_q, a->q, a->dtype, a->bw, a->heads, a->n, q_box_rows)) != FWA2_OK) return rc;
   if ((rc = encode_rows4(&p.tm_k, a->k, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
   if ((rc = encode_rows4(&p.tm_v, a->v, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
-  if ((rc = encode_rows4(&p.tm_do, a->dout, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+  if ((rc = encode_rows4(&p.tm_do, a->dout, a->dtype, a->bw, a->heads, a->n, q_box_rows)) != FWA2_OK) return rc;
   if (has_bias &&
       (rc = encode_table3(&p.tm_biasT, bias_t, a->dtype, a->heads, a->n, a->n, pl.table_pitch)) != FWA2_OK)
     return rc;

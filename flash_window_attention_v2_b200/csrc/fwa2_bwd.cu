@@ -111,6 +111,14 @@ __device__ __forceinline__ int step_rows(const BwdGeom& g, int i, int w) {
   return g.pair ? kStepCols : g.N - kTileRows * i - kStepCols * w;
 }
 
+// Pair mode interleaves the queries of the two units in shared memory (and so in the columns of
+// S^T / dP^T and the lanes of dQ): row r holds query 32 (r / 64) + r % 32 of unit (r / 32) % 2, so
+// that the 64 rows of step w -- the share of warpgroup w -- are the queries [32 w, 32 w + 32) of
+// unit A followed by the same queries of unit B.  Each warpgroup then depends only on its own
+// step, as it does for larger windows.
+__device__ __forceinline__ int pair_row_unit(uint32_t r) { return static_cast<int>((r >> 5) & 1u); }
+__device__ __forceinline__ int pair_row_query(uint32_t r) { return static_cast<int>(32u * (r >> 6) + (r & 31u)); }
+
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
                "f"(d)
@@ -216,9 +224,9 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   // load latency is hidden behind a whole step of compute ----
   auto load_o_row = [&](const TileIt& it, uint4 (&dst)[4], float& lse_out) {
     if (wg == 1) {
-      const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
+      const int m = g.pair ? pair_row_unit(lt) : 0;
       const int bw = bwd_bw(p, g, it.t, m);
-      const int ig = g.pair ? static_cast<int>(lt & 63u) : it.i * kTileRows + static_cast<int>(lt);
+      const int ig = g.pair ? pair_row_query(lt) : it.i * kTileRows + static_cast<int>(lt);
       if (bw < p.BW && ig < g.N) {
         const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
 #pragma unroll
@@ -236,9 +244,9 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       normalise_row<T>(q_base, lt);
       fence_proxy_async_smem();
     } else {
-      const int m = g.pair ? static_cast<int>(lt >> 6) : 0;
+      const int m = g.pair ? pair_row_unit(lt) : 0;
       const int bw = bwd_bw(p, g, it.t, m);
-      const int ig = g.pair ? static_cast<int>(lt & 63u) : it.i * kTileRows + static_cast<int>(lt);
+      const int ig = g.pair ? pair_row_query(lt) : it.i * kTileRows + static_cast<int>(lt);
       float l2 = INFINITY, dl = 0.f;
       if (bw < p.BW && ig < g.N) {
         float dlp[4] = {0.f, 0.f, 0.f, 0.f};
@@ -360,11 +368,11 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   // passes (the tensor-memory loads are warp-wide), only the global accesses are predicated.
   auto dq_epilogue = [&](int t_e, uint32_t kq) -> bool {
     if (single_tile && wg == 1) return true;
-    const int mq = g.pair ? static_cast<int>(lt >> 6) : 0;
+    const int mq = g.pair ? pair_row_unit(lt) : 0;
     const int bwq = bwd_bw(p, g, t_e, mq);
     uint4 qraw[4];
     auto load_q = [&](int i) -> bool {
-      const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
+      const int ig = g.pair ? pair_row_query(lt) : i * kTileRows + static_cast<int>(lt);
       const bool okq = bwq < p.BW && ig < g.N;
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) qraw[ch] = make_uint4(0u, 0u, 0u, 0u);
@@ -383,7 +391,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     trace_ev(tr, 12);
 #pragma unroll 1
     for (int i = static_cast<int>(wg); i < g.MT; i += 2) {
-      const int ig = g.pair ? static_cast<int>(lt & 63u) : i * kTileRows + static_cast<int>(lt);
+      const int ig = g.pair ? pair_row_query(lt) : i * kTileRows + static_cast<int>(lt);
       const uint32_t t_dq = tmem + lane_base + tm_dq(nsets, set, static_cast<uint32_t>(i));
       float ss = 0.f, qd = 0.f;
 #pragma unroll
@@ -473,13 +481,12 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
 
     trace_ev(tr, 2);
     // ------------------------------ my share of the current tile ------------------------------
-    // Windows of more than 64 tokens: warpgroup w takes step w (queries [64 w, 64 w + 64)) in two
-    // chunks.  Pair mode: only the diagonal blocks (keys and queries of the same unit) carry work,
-    // so the warps whose lanes hold the keys of unit m take the queries of unit m (step m), and
-    // the two warpgroups split them: warpgroup w takes chunk w.  The off-diagonal block of the
-    // same lanes and chunk in the other step is filled with zeros.
+    // Warpgroup w takes step w (64 queries) of the tile.  Windows of more than 64 tokens: in two
+    // chunks of 32 queries.  Pair mode: the step holds 32 queries of unit A and 32 of unit B, and
+    // only the diagonal blocks (keys and queries of the same unit) carry work, so a thread takes
+    // the one chunk of its key's unit and fills its part of the other chunk with zeros.
     const uint32_t um = lt >> 6;                       // pair mode: unit of my key
-    const uint32_t step = g.pair ? um : wg;
+    const uint32_t step = wg;
     const int nr = step_rows(g, cur.i, static_cast<int>(step));
     const uint32_t kvs = kv_ring.stage;
     if (nr > 0) {
@@ -508,7 +515,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       const bool db_store = (jt == 0);
       const uint32_t tm_st = tmem + lane_base + step * 128u + kTmST;
       const uint32_t tm_dpt = tmem + lane_base + step * 128u + kTmDPT;
-      const int c_first = g.pair ? static_cast<int>(wg) : 0, c_last = g.pair ? static_cast<int>(wg) : 1;
+      const int c_first = g.pair ? static_cast<int>(um) : 0, c_last = g.pair ? static_cast<int>(um) : 1;
 
 #pragma unroll 1
       for (int c = c_first; c <= c_last; ++c) {
@@ -519,20 +526,20 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           tc_fence_after();
           trace_ev(tr, 3);
           if (g.pair) {
-            // the other unit's queries must not see my key: zeros in the other step, same chunk
-            // (issued now, so that the stores drain while this chunk is being computed)
-            const uint32_t other = step ^ 1u;
-            if (!mbar_wait(bar(kbStFull + 2 * other + c), (nst >> c) & 1u, ctx, 57)) return;
+            // the other unit's queries must not see my key: zeros in the other chunk of the step
+            // (issued now, so that the stores drain while my chunk is being computed)
+            const uint32_t oc = static_cast<uint32_t>(c) ^ 1u;
+            if (!mbar_wait(bar(kbStFull + 2 * step + oc), (nst >> c) & 1u, ctx, 57)) return;
             tc_fence_after();
             uint32_t z[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) z[i] = 0u;
-            tmem_st16(tmem + lane_base + other * 128u + kTmST + 32u * c, z);
-            tmem_st16(tmem + lane_base + other * 128u + kTmDPT + 32u * c, z);
+            tmem_st16(tm_st + 32u * oc, z);
+            tmem_st16(tm_dpt + 32u * oc, z);
             const uint32_t z4[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd)
-              sts128(ds_tile + other * 16384u + sw128_offset(lt, 4u * c + qd), z4);
+              sts128(ds_slab + sw128_offset(lt, 4u * oc + qd), z4);
           }
           uint32_t bias_tile = 0, mask_tile = 0;
           const uint32_t st = bm_ring.stage;
@@ -594,7 +601,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
         tc_fence_before();
         fence_proxy_async_smem();
         mbar_arrive(bar(kbPtFull + 2 * step + c));
-        if (g.pair) mbar_arrive(bar(kbPtFull + 2 * (step ^ 1u) + c));
+        if (g.pair) mbar_arrive(bar(kbPtFull + 2 * step + (c ^ 1)));
         nst ^= 1u << c;
         trace_ev(tr, 8);
       }
@@ -754,11 +761,13 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
       }
     }
     // chunks in the order in which the two warpgroups finish them: (w0,c0) (w1,c0) (w0,c1) (w1,c1)
+    // Pair mode: both chunks of a step come from the same warpgroup at the same time, so the step
+    // is finished (and the next tile's scores of that warpgroup issued) before the other is looked at.
     bool looked = false;
 #pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-#pragma unroll 1
-      for (int w = 0; w < 2; ++w) {
+    for (int idx = 0; idx < 4; ++idx) {
+      {
+        const int c = g.pair ? (idx & 1) : (idx >> 1), w = g.pair ? (idx >> 1) : (idx & 1);
         if (chunk_exists(cur, w, c)) {
           const int bi = 2 * w + c;
           if (!mbar_wait(bar(kbPtFull + bi), (nst >> bi) & 1u, ctx, 64)) return;
@@ -779,9 +788,9 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
             // dBias^T += dS^T * I: the tensor core sums over the windows of this CTA
 #pragma unroll
             for (uint32_t k = 0; k < 2; ++k)
-              mma_ts(tmem + tm_db(static_cast<uint32_t>(c)), a_ds + k * 8u, desc_at(dm64, ident + k * 1024u), idesc_acc,
-                     db_started[c] | k);
-            db_started[c] = 1u;
+              mma_ts(tmem + tm_db(static_cast<uint32_t>(w)), a_ds + k * 8u, desc_at(dm64, ident + k * 1024u), idesc_acc,
+                     db_started[w] | k | static_cast<uint32_t>(c));
+            if (c == 1) db_started[w] = 1u;
           }
         }
         // the next tile's scores of step w go over this tile's P^T / dS^T of both chunks
@@ -874,12 +883,16 @@ __device__ void bwd_load_main(const BwdParams& p, uint32_t smem_base, uint32_t b
       const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
       const uint32_t full = bar(kbQdoFull + qs);
       mbar_arrive_expect_tx(full, kQdoStageBytes);
+      // two boxes of 64 rows; pair mode: four boxes of 32 rows, unit A and unit B alternating
+      // (see pair_row_unit / pair_row_query)
+      const int nb = g.pair ? 4 : 2;
+      const uint32_t box_bytes = g.pair ? kBoxBytes / 2u : kBoxBytes;
 #pragma unroll 1
-      for (int b = 0; b < 2; ++b) {
-        const int bw = bwd_bw(p, g, it.t, g.pair ? b : 0);
-        const int r0 = g.pair ? 0 : it.i * kTileRows + b * kBoxRows;
-        tma_load_4d(q_base + b * kBoxBytes, &p.tm_q, full, 0, r0, g.h, bw);
-        tma_load_4d(q_base + 2u * kBoxBytes + b * kBoxBytes, &p.tm_do, full, 0, r0, g.h, bw);
+      for (int b = 0; b < nb; ++b) {
+        const int bw = bwd_bw(p, g, it.t, g.pair ? (b & 1) : 0);
+        const int r0 = g.pair ? 32 * (b >> 1) : it.i * kTileRows + b * kBoxRows;
+        tma_load_4d(q_base + b * box_bytes, &p.tm_q, full, 0, r0, g.h, bw);
+        tma_load_4d(q_base + 2u * kBoxBytes + b * box_bytes, &p.tm_do, full, 0, r0, g.h, bw);
       }
       qdo.advance();
     }
