@@ -8,8 +8,9 @@
 //
 // One persistent CTA per SM.  A tile is 128 keys x 128 queries; its two 64-query halves
 // ("steps") are processed concurrently by two warpgroups.  Roles:
-//   warps 0-3   warpgroup 0: thread t owns key t of the tile, queries [0, 64)
-//   warps 4-7   warpgroup 1: same keys, queries [64, 128)
+//   warps 0-3   compute warpgroup 0: thread t owns key t of the tile, queries [0, 64)
+//   warps 4-7   compute warpgroup 1: same keys, queries [64, 128)
+//   warps 12-15 preparing warpgroup: normalises K and Q, computes delta, one tile ahead
 //   warp  8     issues every tcgen05.mma (one thread)
 //   warp  9     TMA producer of K/V and Q/dO (one thread)
 //   warps 10-11 TMA producers of the bias / mask tables of warpgroup 0 / 1 (one thread each)
@@ -19,7 +20,7 @@
 #define FWA2_BWD_NORMALISE_ROLLED 1
 #endif
 #ifndef FWA2_BWD_WAIT_INLINE
-#define FWA2_BWD_WAIT_INLINE 0
+#define FWA2_BWD_WAIT_INLINE 1   // register reallocation (setmaxnreg) does not go with calls
 #endif
 #define FWA2_NORMALISE_ROLLED FWA2_BWD_NORMALISE_ROLLED
 #define FWA2_WAIT_INLINE FWA2_BWD_WAIT_INLINE
@@ -27,7 +28,7 @@
 
 namespace fwa2 {
 
-constexpr int kBwdThreads = 384;
+constexpr int kBwdThreads = 512;
 constexpr uint32_t kBwdTmemCols = 512;
 constexpr uint32_t kTmST = 0;       // S^T of warpgroup w at 128 w (64 columns), P^T written over it
 constexpr uint32_t kTmDPT = 64;     // dP^T of warpgroup w at 128 w + 64, dS^T written over it
@@ -203,74 +204,10 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   float* rowstats = reinterpret_cast<float*>(smem_ptr + p.off_rowstats);
   const uint32_t NKV = p.n_kv_stages, NDS = p.n_ds_bufs, NBM = p.n_bm_stages;
 
-  // Jobs of a single tile (windows of at most 128 tokens) split the per-job work by kind instead
-  // of by half: warpgroup 1 normalises K and writes dV and dK, warpgroup 0 normalises Q and writes
-  // dQ (the barriers are initialised with the matching arrival counts).
+  // Warpgroup 0 writes dV, warpgroup 1 writes dK.  dQ: warpgroup (i mod 2) writes query tile i, so
+  // for jobs of a single tile (windows of at most 128 tokens) warpgroup 0 alone (its barrier is
+  // initialised with the matching arrival count).
   const bool single_tile = (g.KB * g.MT == 1);
-  // ---- K of a job: normalise in place, remember 1 / |k| ----
-  auto prologue_job = [&](const Ring& r) -> bool {
-    // a single tile of keys is left to warpgroup 1 (warpgroup 0 normalises Q meanwhile)
-    if (single_tile && wg == 0) return true;
-    const uint32_t kvs = r.stage;
-    const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
-    if (!mbar_wait(bar(kbKvFull + kvs), r.phase, ctx, 50)) return false;
-    for (uint32_t rr = single_tile ? lt : tid; rr < static_cast<uint32_t>(p.rows_kv); rr += 256u)
-      rk_arr[kvs * p.rows_kv + rr] = normalise_row<T>(k_base, rr);
-    fence_proxy_async_smem();
-    mbar_arrive(bar(kbKvReady + kvs));
-    return true;
-  };
-  // ---- O row of a query (warpgroup 1 only): issued one tile ahead of its use so that the global
-  // load latency is hidden behind a whole step of compute ----
-  auto load_o_row = [&](const TileIt& it, uint4 (&dst)[4], float& lse_out) {
-    if (wg == 1) {
-      const int m = g.pair ? pair_row_unit(lt) : 0;
-      const int bw = bwd_bw(p, g, it.t, m);
-      const int ig = g.pair ? pair_row_query(lt) : it.i * kTileRows + static_cast<int>(lt);
-      if (bw < p.BW && ig < g.N) {
-        const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) dst[ch] = ldg_nc_v4(orow + ch * 8);
-        lse_out = __ldg(p.lse + bw * p.lse_sbw + g.h * p.lse_sh + ig);
-      }
-    }
-  };
-  // ---- Q / dO of a query tile: warpgroup 0 normalises Q, warpgroup 1 computes delta and lse ----
-  auto prologue_tile = [&](const TileIt& it, const Ring& r, const uint4 (&o_row)[4], float lse) -> bool {
-    const uint32_t qs = r.stage;
-    const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
-    if (!mbar_wait(bar(kbQdoFull + qs), r.phase, ctx, 51)) return false;
-    if (wg == 0) {
-      normalise_row<T>(q_base, lt);
-      fence_proxy_async_smem();
-    } else {
-      const int m = g.pair ? pair_row_unit(lt) : 0;
-      const int bw = bwd_bw(p, g, it.t, m);
-      const int ig = g.pair ? pair_row_query(lt) : it.i * kTileRows + static_cast<int>(lt);
-      float l2 = INFINITY, dl = 0.f;
-      if (bw < p.BW && ig < g.N) {
-        float dlp[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t wd[4];
-          lds128(q_base + 2u * kBoxBytes + sw64_offset(lt, ch), wd);
-          const uint32_t wo[4] = {o_row[ch].x, o_row[ch].y, o_row[ch].z, o_row[ch].w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            dlp[ch] = fmaf(Elem<T>::lo(wd[i]), Elem<T>::lo(wo[i]), dlp[ch]);
-            dlp[ch] = fmaf(Elem<T>::hi(wd[i]), Elem<T>::hi(wo[i]), dlp[ch]);
-          }
-        }
-        dl = (dlp[0] + dlp[1]) + (dlp[2] + dlp[3]);
-        l2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
-      }
-      rowstats[qs * 256u + lt] = l2;
-      rowstats[qs * 256u + 128u + lt] = dl;
-    }
-    mbar_arrive(bar(kbQdoReady + qs));
-    return true;
-  };
-
   const uint32_t nsets = bwd_num_sets(p, g.KB, g.MT);
   const uint32_t sets_mask = nsets - 1u, sets_shift = nsets - 1u;
   uint32_t jt = 0, kdkv = 0, kdq = 0;
@@ -279,7 +216,6 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   TraceCursor tr = (lt == 0) ? trace_begin(p.trace, wg == 0 ? 0 : 3) : TraceCursor{nullptr, 0};
   // ---- dK, dV of one key block (thread = key): warpgroup 0 writes dV, warpgroup 1 writes dK ----
   auto dkv_epilogue = [&](const TileIt& it, uint32_t kvs_e, uint32_t kd) -> bool {
-    if (single_tile && wg == 0) return true;
     // dK, dV of key block it.j are complete
     const uint32_t set = kd & sets_mask, use = kd >> sets_shift;
     if (!mbar_wait(bar(kbDkvFull + set), use & 1u, ctx, 55)) return false;
@@ -290,7 +226,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     const int jg = g.pair ? static_cast<int>(lt & 63u) : it.j * kTileRows + static_cast<int>(lt);
     const bool ok = bw < p.BW && jg < g.N;
     // (rolled loops over groups of eight columns: see bwd_group about code size)
-    if (wg == 0 || single_tile) {
+    if (wg == 0) {
       uint16_t* dst = static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + jg * p.dv_sn;
       const uint32_t t_dv = tmem + lane_base + tm_dv(set);
 #pragma unroll 1
@@ -307,10 +243,8 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           *reinterpret_cast<uint4*>(dst + 8u * gq) = v;
         }
       }
-      if (wg == 0) {
-        tc_fence_before();
-        mbar_arrive(bar(kbDkvFree + set));
-      }
+      tc_fence_before();
+      mbar_arrive(bar(kbDkvFree + set));
     }
     if (wg == 1) {
       // dk = scale * (dK' - k^ (k^ . dK')) / |k|: one pass for the dot product, one for the output
@@ -446,39 +380,17 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   int pq_t = 0;
 
   TileIt cur{0, 0, 0};
-  uint4 o_row[4] = {};
-  float lse_pf = 0.f;
-  load_o_row(cur, o_row, lse_pf);
-  if (!prologue_job(kv_ring)) return;
-  if (!prologue_tile(cur, qdo_ring, o_row, lse_pf)) return;
-  {
-    TileIt t1 = cur;
-    if (tile_next(g, t1)) load_o_row(t1, o_row, lse_pf);
-  }
-
   while (true) {
     TileIt nxt = cur;
     const bool has_next = tile_next(g, nxt);
-    // With two K/V stages the next job's K is normalised one tile ahead of its first use; with a
-    // single stage its load can only start once this job is finished, so it is done at the end.
-    bool defer_job = false;
     trace_ev(tr, 1);
     Ring kv_next = kv_ring, qdo_next = qdo_ring;
     kv_next.advance();
     qdo_next.advance();
-    if (has_next) {
-      if (nxt.t != cur.t) {
-        if (NKV >= 2) {
-          if (!prologue_job(kv_next)) return;
-        } else {
-          defer_job = true;
-        }
-      }
-      if (!prologue_tile(nxt, qdo_next, o_row, lse_pf)) return;
-      TileIt nxt2 = nxt;
-      if (tile_next(g, nxt2)) load_o_row(nxt2, o_row, lse_pf);
-    }
-
+    // what the preparing warpgroup wrote for this tile and job (row statistics, 1 / |k|) is
+    // visible once its barriers have been seen; both completed long ago
+    if (!mbar_wait(bar(kbKvReady + kv_ring.stage), kv_ring.phase, ctx, 50)) return;
+    if (!mbar_wait(bar(kbQdoReady + qdo_ring.stage), qdo_ring.phase, ctx, 51)) return;
     trace_ev(tr, 2);
     // ------------------------------ my share of the current tile ------------------------------
     // Warpgroup w takes step w (64 queries) of the tile.  Windows of more than 64 tokens: in two
@@ -522,15 +434,15 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
         const int rows_left = nr - kChunkCols * c;
         if (rows_left > 0) {
           // scores of this chunk (the tensor core is meanwhile working on the other chunks)
-          if (!mbar_wait(bar(kbStFull + 2 * step + c), (nst >> c) & 1u, ctx, 52)) return;
+          // (pair mode: one barrier per step, both chunks are produced and consumed together)
+          const int bc = g.pair ? 0 : c;
+          if (!mbar_wait(bar(kbStFull + 2 * step + bc), (nst >> bc) & 1u, ctx, 52)) return;
           tc_fence_after();
           trace_ev(tr, 3);
           if (g.pair) {
             // the other unit's queries must not see my key: zeros in the other chunk of the step
             // (issued now, so that the stores drain while my chunk is being computed)
             const uint32_t oc = static_cast<uint32_t>(c) ^ 1u;
-            if (!mbar_wait(bar(kbStFull + 2 * step + oc), (nst >> c) & 1u, ctx, 57)) return;
-            tc_fence_after();
             uint32_t z[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) z[i] = 0u;
@@ -558,17 +470,20 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           const float* lse2_c = lse2 + 32 * c;
           const float* delta_c = delta + 32 * c;
           float* dbp = db_row != nullptr ? db_row + kChunkCols * c : nullptr;
-          // four groups of eight queries, two per trip; the scores of the next group are fetched
-          // from tensor memory while the current one is computed
+          // four groups of eight queries; the scores of the next group are fetched from tensor
+          // memory while the current one is computed (one copy of the group's code: the register
+          // moves that rotate the buffers are cheaper than a second copy in the instruction cache)
           uint32_t sa[8], da[8], sb[8], db8[8];
           tmem_ld8(t_s, sa);
           tmem_ld8(t_d, da);
 #pragma unroll 1
-          for (uint32_t gq = 0; gq < 4u; gq += 2u) {
+          for (uint32_t gq = 0; gq < 4u; ++gq) {
             uint32_t pw[4], dw[4];
             tmem_wait_ld();
-            tmem_ld8(t_s + 8u * (gq + 1u), sb);
-            tmem_ld8(t_d + 8u * (gq + 1u), db8);
+            if (gq + 1u < 4u) {
+              tmem_ld8(t_s + 8u * (gq + 1u), sb);
+              tmem_ld8(t_d + 8u * (gq + 1u), db8);
+            }
             bwd_group<T>(p.has_bias, p.has_mask, sa, da, bias_base + ((gq ^ bias_sw) << 4),
                          mask_base + ((gq ^ mask_sw) << 4), lse2_c + 8u * gq, delta_c + 8u * gq, scale,
                          key_ok, dbp != nullptr ? dbp + 8u * gq : nullptr, db_store, pw, dw);
@@ -576,18 +491,11 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
             tmem_st4(t_s + 4u * gq, pw);
             tmem_st4(t_d + 4u * gq, dw);
             sts128(ds_base + (((4u * c + gq) ^ ds_sw) << 4), dw);
-            tmem_wait_ld();
-            if (gq + 2u < 4u) {
-              tmem_ld8(t_s + 8u * (gq + 2u), sa);
-              tmem_ld8(t_d + 8u * (gq + 2u), da);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              sa[i] = sb[i];
+              da[i] = db8[i];
             }
-            bwd_group<T>(p.has_bias, p.has_mask, sb, db8, bias_base + (((gq + 1u) ^ bias_sw) << 4),
-                         mask_base + (((gq + 1u) ^ mask_sw) << 4), lse2_c + 8u * (gq + 1u),
-                         delta_c + 8u * (gq + 1u), scale, key_ok,
-                         dbp != nullptr ? dbp + 8u * (gq + 1u) : nullptr, db_store, pw, dw);
-            tmem_st4(t_s + 4u * (gq + 1u), pw);
-            tmem_st4(t_d + 4u * (gq + 1u), dw);
-            sts128(ds_base + (((4u * c + gq + 1u) ^ ds_sw) << 4), dw);
           }
           trace_ev(tr, 7);
           if (any_table) {
@@ -600,9 +508,8 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
         tmem_wait_st();
         tc_fence_before();
         fence_proxy_async_smem();
-        mbar_arrive(bar(kbPtFull + 2 * step + c));
-        if (g.pair) mbar_arrive(bar(kbPtFull + 2 * step + (c ^ 1)));
-        nst ^= 1u << c;
+        mbar_arrive(bar(kbPtFull + 2 * step + (g.pair ? 0 : c)));
+        nst ^= 1u << (g.pair ? 0 : c);
         trace_ev(tr, 8);
       }
       trace_ev(tr, 9);
@@ -635,9 +542,6 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     if (last_k) ++kdq;
 
     if (!has_next) break;
-    if (defer_job) {
-      if (!prologue_job(kv_next)) return;
-    }
     if (nxt.t != cur.t) {
       ++jt;
       kv_ring = kv_next;
@@ -668,6 +572,98 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       }
     }
     tc_fence_before();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The preparing warpgroup (thread = row): everything a tile needs before its scores can be
+// computed, one tile ahead of the compute warpgroups and off their critical path.
+//   per job:   K rows normalised in place, 1 / |k| kept for the dK epilogue
+//   per tile:  Q row normalised in place; delta = dO . O and lse * log2(e) of the row
+// The O row comes straight from global memory, fetched one tile ahead into registers.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ void bwd_prepare_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t smem_base,
+                                 uint32_t bars, const WaitCtx& ctx) {
+  const BwdGeom g = bwd_geom(p);
+  if (g.njobs == 0) return;
+  const uint32_t lt = threadIdx.x & 127u;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  float* rk_arr = reinterpret_cast<float*>(smem_ptr + p.off_rk);
+  float* rowstats = reinterpret_cast<float*>(smem_ptr + p.off_rowstats);
+
+  struct ORow {
+    uint4 v[4];
+    float lse;
+    bool ok;
+  };
+  auto load_o_row = [&](const TileIt& it, ORow& dst) {
+    const int m = g.pair ? pair_row_unit(lt) : 0;
+    const int bw = bwd_bw(p, g, it.t, m);
+    const int ig = g.pair ? pair_row_query(lt) : it.i * kTileRows + static_cast<int>(lt);
+    dst.ok = bw < p.BW && ig < g.N;
+    if (dst.ok) {
+      const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) dst.v[ch] = ldg_nc_v4(orow + ch * 8);
+      dst.lse = __ldg(p.lse + bw * p.lse_sbw + g.h * p.lse_sh + ig);
+    }
+  };
+
+  TileIt it{0, 0, 0};
+  Ring kv(p.n_kv_stages), qdo(kNumQdoStages);
+  bool new_job = true;
+  ORow o_cur{}, o_next{};
+  load_o_row(it, o_cur);
+#pragma unroll 1
+  while (true) {
+    TileIt nx = it;
+    const bool has_next = tile_next(g, nx);
+    if (has_next) load_o_row(nx, o_next);
+
+    if (new_job) {
+      const uint32_t kvs = kv.stage;
+      const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
+      if (!mbar_wait(bar(kbKvFull + kvs), kv.phase, ctx, 80)) return;
+#pragma unroll 1
+      for (uint32_t rr = lt; rr < static_cast<uint32_t>(p.rows_kv); rr += 128u)
+        rk_arr[kvs * p.rows_kv + rr] = normalise_row<T>(k_base, rr);
+      fence_proxy_async_smem();
+      mbar_arrive(bar(kbKvReady + kvs));
+    }
+    {
+      const uint32_t qs = qdo.stage;
+      const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
+      if (!mbar_wait(bar(kbQdoFull + qs), qdo.phase, ctx, 81)) return;
+      normalise_row<T>(q_base, lt);
+      fence_proxy_async_smem();
+      float l2 = INFINITY, dl = 0.f;
+      if (o_cur.ok) {
+        float dlp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t wd[4];
+          lds128(q_base + 2u * kBoxBytes + sw64_offset(lt, ch), wd);
+          const uint32_t wo[4] = {o_cur.v[ch].x, o_cur.v[ch].y, o_cur.v[ch].z, o_cur.v[ch].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            dlp[ch] = fmaf(Elem<T>::lo(wd[i]), Elem<T>::lo(wo[i]), dlp[ch]);
+            dlp[ch] = fmaf(Elem<T>::hi(wd[i]), Elem<T>::hi(wo[i]), dlp[ch]);
+          }
+        }
+        dl = (dlp[0] + dlp[1]) + (dlp[2] + dlp[3]);
+        l2 = (o_cur.lse == -INFINITY) ? INFINITY : o_cur.lse * kLog2e;
+      }
+      rowstats[qs * 256u + lt] = l2;
+      rowstats[qs * 256u + 128u + lt] = dl;
+      mbar_arrive(bar(kbQdoReady + qs));
+    }
+    if (!has_next) break;
+    new_job = nx.t != it.t;
+    if (new_job) kv.advance();
+    qdo.advance();
+    it = nx;
+    o_cur = o_next;
   }
 }
 
@@ -846,6 +842,117 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
 }
 
 // ------------------------------------------------------------------------------------------------
+// MMA issuer for pair mode (one thread).  Every tile is a job of its own (one key block, one query
+// tile), every chunk exists, and the issuing thread is the busiest in the CTA: the whole tile is
+// written out as straight-line code with as few waits and commits as the dependencies allow.
+// Per step w one barrier announces the scores (kbStFull + 2 w) and one P^T / dS^T (kbPtFull + 2 w).
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
+                                  const WaitCtx& ctx) {
+  const BwdGeom g = bwd_geom(p);
+  if (g.njobs == 0) return;
+  constexpr uint32_t fmt = Elem<T>::kFmt;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const uint32_t NKV = p.n_kv_stages, NDS = p.n_ds_bufs;
+  const uint32_t idesc_acc = make_idesc(fmt, 128, 32, 0, 1);   // A in TMEM, B MN-major
+  const uint32_t idesc_dq = make_idesc(fmt, 128, 32, 1, 1);    // A and B MN-major
+  const uint32_t idesc_s = make_idesc(fmt, 128, kStepCols, 0, 0);
+  const DescBase dk64 = make_desc_base(0, 16, 512, kSw64);      // K-major rows of 64 bytes
+  const DescBase dm64 = make_desc_base(0, 512, 512, kSw64);     // MN-major rows of 64 bytes
+  const DescBase dds = make_desc_base(0, 16384, 1024, kSw128);  // dS tile, MN-major, two slabs
+  const uint32_t nsets = bwd_num_sets(p, 1, 1);
+  const uint32_t sets_mask = nsets - 1u, sets_shift = nsets - 1u;
+  const bool db_in_tmem = p.db_partial != nullptr;
+  const uint32_t ident = smem_base + p.off_ident;
+  const uint32_t kv_bytes = p.kv_stage_bytes, v_off = static_cast<uint32_t>(p.rows_kv) * kRowBytes;
+
+  // S^T = K^ Q^^T and dP^T = V dO^T of step w (64 queries)
+  auto issue_sdp = [&](uint32_t w, uint32_t k_base, uint32_t q_base) {
+    const uint32_t row_off = w * (kStepCols * kRowBytes);
+    const uint32_t st = tmem + w * 128u + kTmST, dpt = tmem + w * 128u + kTmDPT;
+#pragma unroll
+    for (uint32_t k = 0; k < 2u; ++k) {
+      mma_ss(st, desc_at(dk64, k_base + 32u * k), desc_at(dk64, q_base + row_off + 32u * k), idesc_s, k);
+      mma_ss(dpt, desc_at(dk64, k_base + v_off + 32u * k),
+             desc_at(dk64, q_base + 2u * kBoxBytes + row_off + 32u * k), idesc_s, k);
+    }
+    mma_commit(bar(kbStFull + 2 * static_cast<int>(w)));
+  };
+
+  Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS);
+  uint32_t tile = 0, pt_phase = 0, db_started = 0;
+  if (!mbar_wait(bar(kbKvReady + 0), 0u, ctx, 60)) return;
+  if (!mbar_wait(bar(kbQdoReady + 0), 0u, ctx, 61)) return;
+  tc_fence_after();
+  issue_sdp(0u, smem_base + p.off_kv, smem_base + p.off_qdo);
+  issue_sdp(1u, smem_base + p.off_kv, smem_base + p.off_qdo);
+
+#pragma unroll 1
+  for (int t = 0; t < g.njobs; ++t, ++tile) {
+    const bool has_next = t + 1 < g.njobs;
+    Ring kv_next = kv_ring, qdo_next = qdo_ring;
+    kv_next.advance();
+    qdo_next.advance();
+    const uint32_t set = tile & sets_mask, use = tile >> sets_shift;
+    const uint32_t k_base = smem_base + p.off_kv + kv_ring.stage * kv_bytes;
+    const uint32_t q_base = smem_base + p.off_qdo + qdo_ring.stage * kQdoStageBytes;
+    const uint32_t kn_base = smem_base + p.off_kv + kv_next.stage * kv_bytes;
+    const uint32_t qn_base = smem_base + p.off_qdo + qdo_next.stage * kQdoStageBytes;
+    // the accumulators of this set have been read out
+    if (!mbar_wait(bar(kbDkvFree + set), (use & 1u) ^ 1u, ctx, 62)) return;
+    if (!mbar_wait(bar(kbDqFree + set), (use & 1u) ^ 1u, ctx, 63)) return;
+#pragma unroll 1
+    for (uint32_t w = 0; w < 2u; ++w) {
+      if (!mbar_wait(bar(kbPtFull + 2 * static_cast<int>(w)), pt_phase, ctx, 64)) return;
+      tc_fence_after();
+#pragma unroll
+      for (uint32_t c = 0; c < 2u; ++c) {
+        const uint32_t row_off = (w * kStepCols + c * kChunkCols) * kRowBytes;
+        const uint32_t a_p = tmem + w * 128u + kTmST + 32u * c, a_ds = tmem + w * 128u + kTmDPT + 32u * c;
+#pragma unroll
+        for (uint32_t k = 0; k < 2u; ++k) {
+          const uint32_t acc = (w | c | k) ? 1u : 0u;
+          mma_ts(tmem + tm_dv(set), a_p + k * 8u, desc_at(dm64, q_base + 2u * kBoxBytes + row_off + k * 1024u),
+                 idesc_acc, acc);
+          mma_ts(tmem + tm_dk(set), a_ds + k * 8u, desc_at(dm64, q_base + row_off + k * 1024u), idesc_acc, acc);
+          if (db_in_tmem)   // dBias^T += dS^T * I: the tensor core sums over the windows of this CTA
+            mma_ts(tmem + tm_db(w), a_ds + k * 8u, desc_at(dm64, ident + k * 1024u), idesc_acc,
+                   (c | k) ? 1u : db_started);
+        }
+      }
+      // the next tile's scores of step w go over this tile's P^T / dS^T
+      if (has_next) {
+        if (w == 0u) {
+          if (!mbar_wait(bar(kbKvReady + kv_next.stage), kv_next.phase, ctx, 65)) return;
+          if (!mbar_wait(bar(kbQdoReady + qdo_next.stage), qdo_next.phase, ctx, 66)) return;
+          tc_fence_after();
+        }
+        issue_sdp(w, kn_base, qn_base);
+      }
+    }
+    db_started = 1u;
+    pt_phase ^= 1u;
+    // dQ^ += dS K^
+    {
+      const uint32_t ds_base = smem_base + p.off_ds + ds_ring.stage * kDsTileBytes;
+#pragma unroll 2
+      for (uint32_t k = 0; k < 8u; ++k)
+        mma_ss(tmem + tm_dq(nsets, set, 0u), desc_at(dds, ds_base + k * 2048u), desc_at(dm64, k_base + k * 1024u),
+               idesc_dq, k);
+    }
+    mma_commit(bar(kbDsFree + ds_ring.stage));
+    mma_commit(bar(kbQdoFree + qdo_ring.stage));
+    mma_commit(bar(kbDkvFull + set));
+    mma_commit(bar(kbDqFull + set));
+    mma_commit(bar(kbKvFree + kv_ring.stage));
+    kv_ring = kv_next;
+    qdo_ring = qdo_next;
+    ds_ring.advance();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // TMA producers: three warps (one thread each), one stream each, so that none of them ever waits
 // for the consumers of another and each is a short loop of blocking waits:
 //   warp 9   K/V of a job, then Q/dO of each of its tiles
@@ -962,16 +1069,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
   if (tid == 0) {
     ctrl_words[1] = 0u;
     for (int i = 0; i < kBwdNumBars; ++i) {
-      // jobs of a single tile: K is normalised, and dK / dV are written, by warpgroup 1 alone and
-      // dQ by warpgroup 0 alone
+      // jobs of a single tile: dQ is written by warpgroup 0 alone
       const bool single = p.pair_mode || p.N <= kTileRows;
       uint32_t count = 1u;
-      if (i >= kbKvReady && i < kbKvFree) count = single ? 128u : 256u;
-      else if (i >= kbKvFree && i < kbQdoFull) count = single ? 129u : 257u;
-      else if (i >= kbQdoReady && i < kbQdoFree) count = 256u;
+      if (i >= kbKvReady && i < kbKvFree) count = 128u;   // the preparing warpgroup
+      else if (i >= kbKvFree && i < kbQdoFull) count = 257u;
+      else if (i >= kbQdoReady && i < kbQdoFree) count = 128u;
       else if (i >= kbPtFull && i < kbBmFull) count = 128u;   // four chunk barriers
       else if (i >= kbBmFree && i < kbDsFree) count = 128u;
-      else if ((i >= kbDkvFree && i < kbDqFull) || (i >= kbDqFree && i < kBwdNumBars)) count = single ? 128u : 256u;
+      else if (i >= kbDkvFree && i < kbDqFull) count = 256u;
+      else if (i >= kbDqFree && i < kBwdNumBars) count = single ? 128u : 256u;
       mbar_init(bars + 8u * i, count);
     }
     mbar_fence_init();
@@ -1002,7 +1109,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  WaitCtx ctx{&ctrl_words[1], p.status};
+  WaitCtx ctx{&ctrl_words[1], p.status, (p.trace.buf != nullptr && p.trace.cap >= 700) ? p.trace.buf + 2ll * p.trace.cap + 500 : nullptr};
 
 #if FWA2_TRACE
   // per-CTA wall time, clock cycles and SM id in the producer's (otherwise unused) trace region
@@ -1014,12 +1121,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
   }
 #endif
   float dscale_acc = 0.f;
+  // 512 threads start with 128 registers each; the compute warpgroups take what the others give up
   if (warp < 8) {
+    reg_alloc<176>();
     bwd_compute_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, dscale_acc);
-  } else if (lane == 0) {
-    if (warp == 8) bwd_mma_role<T>(p, smem_base, bars, tmem, ctx);
-    else if (warp == 9) bwd_load_main(p, smem_base, bars, ctx);
-    else bwd_load_tables(p, smem_base, bars, ctx, static_cast<int>(warp) - 10);
+  } else if (warp < 12) {
+    reg_dealloc<80>();
+    if (lane == 0) {
+      if (warp == 8) {
+        if (p.pair_mode) bwd_mma_role_pair<T>(p, smem_base, bars, tmem, ctx);
+        else bwd_mma_role<T>(p, smem_base, bars, tmem, ctx);
+      } else if (warp == 9) bwd_load_main(p, smem_base, bars, ctx);
+      else bwd_load_tables(p, smem_base, bars, ctx, static_cast<int>(warp) - 10);
+    }
+  } else {
+    reg_dealloc<80>();
+    bwd_prepare_role<T>(p, smem_raw, smem_base, bars, ctx);
   }
   __syncwarp();
   // deterministic CTA-wide sum of the dLogitScale contributions

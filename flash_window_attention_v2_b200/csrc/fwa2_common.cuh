@@ -25,7 +25,8 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLn100 = 4.605170185988092f;
 
 // Optional timeline of CTA 0: each role appends (clock64 << 8 | event) words to its own region.
-// Only compiled in with -DFWA2_TRACE=1 (a development aid: the extra code costs instruction-cache
+// Only compiled in with -DFWA2_TRACE=2 (-DFWA2_TRACE=1: only per-CTA times and the cycles spent in
+// waits; a development aid: the extra code costs instruction-cache
 // space that the kernels cannot spare); otherwise the trace arguments are accepted and ignored.
 #ifndef FWA2_TRACE
 #define FWA2_TRACE 0
@@ -40,7 +41,7 @@ struct TraceCursor {
 };
 __device__ __forceinline__ TraceCursor trace_begin(const Trace& t, int role) {
   TraceCursor c{nullptr, 0};
-#if FWA2_TRACE
+#if FWA2_TRACE >= 2
   if (t.buf != nullptr && blockIdx.x == 0) {
     c.p = t.buf + static_cast<long long>(role) * t.cap;
     c.left = t.cap;
@@ -49,7 +50,7 @@ __device__ __forceinline__ TraceCursor trace_begin(const Trace& t, int role) {
   return c;
 }
 __device__ __forceinline__ void trace_ev(TraceCursor& c, unsigned int id) {
-#if FWA2_TRACE
+#if FWA2_TRACE >= 2
   if (c.left > 0) {
     *c.p++ = (static_cast<unsigned long long>(clock64()) << 8) | id;
     --c.left;

@@ -727,7 +727,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  WaitCtx ctx{&ctrl_words[1], p.status};
+  WaitCtx ctx{&ctrl_words[1], p.status, nullptr};
 
   if (warp < 4) {
     fwd_softmax_role<T, kPTmem>(p, smem_base, bars, tmem, ctx, scale_tab);

@@ -78,6 +78,7 @@ __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity
 struct WaitCtx {
   volatile uint32_t* abort_flag;   // in shared memory
   DeviceStatus* status;            // in global memory (may be nullptr)
+  unsigned long long* wait_acc;    // development builds (-DFWA2_TRACE=1): cycles waited per site, CTA 0
 };
 
 // About one second at ~1.9 GHz: far beyond any legitimate wait in these kernels.
@@ -112,6 +113,20 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 #endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           uint32_t site) {
+#if defined(FWA2_TRACE) && FWA2_TRACE
+  // cycles spent waiting, per site, for one warp of each role of CTA 0 (second compute
+  // warpgroup: site + 100)
+  {
+    const long long w0 = clock64();
+    bool done = false;
+    for (long long it = 0; it < (1ll << 26) && !done; ++it) done = mbar_try_wait(bar, parity);
+    const uint32_t warp = threadIdx.x >> 5;
+    if (ctx.wait_acc != nullptr && blockIdx.x == 0 && (threadIdx.x & 31u) == 0u &&
+        (warp == 0u || warp == 4u || (warp >= 8u && warp <= 12u)))
+      atomicAdd(ctx.wait_acc + site + (warp == 4u ? 100u : 0u), static_cast<unsigned long long>(clock64() - w0));
+    return done;
+  }
+#endif
   if (mbar_try_wait(bar, parity)) return true;
 #if FWA2_WAIT_INLINE
   const long long t0 = clock64();

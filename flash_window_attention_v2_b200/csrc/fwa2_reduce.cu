@@ -73,12 +73,14 @@ __device__ __forceinline__ int units_of(const ReduceParams& p, int s, int w) {
 }
 
 // One block sums an 8 (key) x 32 (query) patch of every partial buffer of its head.  The buffer list
-// is dealt round-robin to eight thread rows (threadIdx.y), each of which adds its buffers in
-// ascending order; the eight sub-sums are then added in ascending order as well, so the result
-// does not depend on timing.
+// is dealt round-robin to kReduceLanes thread rows (threadIdx.y), each of which adds its buffers in
+// ascending order; the sub-sums are then added in ascending order as well, so the result does not
+// depend on timing.  Many thread rows keep the chain of dependent loads per thread short: the
+// kernel is a few microseconds of latency, not bandwidth.
+constexpr int kReduceLanes = 32;
 template <typename T>
-__global__ void __launch_bounds__(256) reduce_partials_kernel(const ReduceParams p) {
-  __shared__ float part[8][8][33];   // [buffer lane][key][query]
+__global__ void __launch_bounds__(32 * kReduceLanes) reduce_partials_kernel(const ReduceParams p) {
+  __shared__ float part[kReduceLanes][8][33];   // [buffer lane][key][query]
   const int h = blockIdx.z;
   const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 8;
   const int tx = threadIdx.x, ty = threadIdx.y;
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(const ReduceParams
     const int nw = p.pair ? 2 : 1;
     const int nbuf = p.nslots * nw;
     const int i = i0 + tx;
-    for (int b = ty; b < nbuf; b += 8) {
+    for (int b = ty; b < nbuf; b += kReduceLanes) {
       const int s = b / nw, w = b - s * nw;
       if (units_of(p, s, w) == 0) continue;
       const long long buf = static_cast<long long>(s * p.H + h) * nw + w;
@@ -105,21 +107,25 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(const ReduceParams
 #pragma unroll
     for (int r = 0; r < 8; ++r) part[ty][r][tx] = acc[r];
     __syncthreads();
-    // thread (tx, ty) finishes key j0 + ty, query i0 + tx
+    // thread (tx, ty < 8) finishes key j0 + ty, query i0 + tx
     float v = 0.f;
+    if (ty < 8) {
 #pragma unroll
-    for (int l = 0; l < 8; ++l) v += part[l][ty][tx];
+      for (int l = 0; l < kReduceLanes; ++l) v += part[l][ty][tx];
+    }
     __syncthreads();
-    part[0][ty][tx] = v;
+    if (ty < 8) part[0][ty][tx] = v;
     __syncthreads();
     // write transposed: out[h][query][key], eight consecutive keys per query
-    const int q = ty * 4 + (tx >> 3), kk = tx & 7;   // 32 queries x 8 keys
-    const int qi = i0 + q, kj = j0 + kk;
-    if (qi < p.N && kj < p.N) {
-      const float o = part[0][kk][q];
-      const long long idx = (static_cast<long long>(h) * p.N + qi) * p.N + kj;
-      if (p.out_f32 != nullptr) p.out_f32[idx] = o;
-      else if (p.dbias != nullptr) static_cast<uint16_t*>(p.dbias)[idx] = to_raw16<T>(o);
+    if (ty < 8) {
+      const int q = ty * 4 + (tx >> 3), kk = tx & 7;   // 32 queries x 8 keys
+      const int qi = i0 + q, kj = j0 + kk;
+      if (qi < p.N && kj < p.N) {
+        const float o = part[0][kk][q];
+        const long long idx = (static_cast<long long>(h) * p.N + qi) * p.N + kj;
+        if (p.out_f32 != nullptr) p.out_f32[idx] = o;
+        else if (p.dbias != nullptr) static_cast<uint16_t*>(p.dbias)[idx] = to_raw16<T>(o);
+      }
     }
   }
   if (blockIdx.x == 0 && blockIdx.y == 0 && tx == 0 && ty == 0 && p.dscale_partial != nullptr) {
@@ -161,7 +167,7 @@ cudaError_t launch_transpose_tables(const void* bias, long long bias_pitch, void
 }
 
 cudaError_t launch_reduce_partials(const ReduceParams& p, int dtype_is_bf16, cudaStream_t stream) {
-  dim3 grid(1, 1, p.H), block(32, 8);
+  dim3 grid(1, 1, p.H), block(32, kReduceLanes);
   if (p.db_partial != nullptr) {
     grid.x = (p.N + 31) / 32;
     grid.y = (p.N + 7) / 8;
