@@ -368,7 +368,7 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   const bool any_table = has_bias || has_mask;
   auto total = [&](uint32_t nkv, uint32_t nds, uint32_t nbm) {
     return nkv * p.kv_stage_bytes + qdo_bytes + nds * 32768u + (any_table ? 2u * nbm * bm_stage : 0u) +
-           2048u + nkv * static_cast<uint32_t>(p.rows_kv) * 4u + 3u * 1024u + kCtrlBytes;
+           4096u + nkv * static_cast<uint32_t>(p.rows_kv) * 4u + 3u * 1024u + kCtrlBytes;
   };
   const uint32_t budget = static_cast<uint32_t>(dev.max_smem_optin);
   // preference order; a job of one tile (at most 128 keys) wants three K/V stages, see
@@ -394,7 +394,7 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   p.off_ds = p.off_qdo + qdo_bytes;
   p.off_bm = p.off_ds + nds * 32768u;
   p.off_ident = p.off_bm + (any_table ? 2u * nbm * bm_stage : 0u);
-  p.off_rk = p.off_ident + 2048u;
+  p.off_rk = p.off_ident + 4096u;
   p.off_rowstats = p.off_rk + nkv * static_cast<uint32_t>(p.rows_kv) * 4u;
   p.off_ctrl = p.off_rowstats + 3u * 1024u;
   p.smem_bytes = p.off_ctrl + kCtrlBytes;

@@ -379,6 +379,17 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   uint32_t pd_kvs = 0, pd_k = 0, pq_k = 0;
   int pq_t = 0;
 
+  if (g.pair && p.db_partial != nullptr) {
+    // the dBias^T sums in tensor memory start from zero (warpgroup w owns the columns of step w;
+    // the first product that adds to them is issued after this warpgroup's first P^T barrier)
+    uint32_t z[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) z[i] = 0u;
+    tmem_st16(tmem + lane_base + tm_db(wg), z);
+    tmem_st16(tmem + lane_base + tm_db(wg) + 16u, z);
+    tmem_wait_st();
+    tc_fence_before();
+  }
   TileIt cur{0, 0, 0};
   while (true) {
     TileIt nxt = cur;
@@ -722,9 +733,6 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
   const uint32_t sets_mask = nsets - 1u, sets_shift = nsets - 1u;
   TraceCursor tr = trace_begin(p.trace, 1);
   uint32_t nst = 0u;   // phase bit per (2 * warpgroup + chunk)
-  const bool db_in_tmem = g.pair && p.db_partial != nullptr;
-  const uint32_t ident = smem_base + p.off_ident;
-  uint32_t db_started[2] = {0u, 0u};
   Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS);
   TileIt cur{0, 0, 0};
   if (!mbar_wait(bar(kbKvReady + 0), 0u, ctx, 60)) return;
@@ -779,14 +787,6 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
                    idesc_acc, first | k);
             mma_ts(tmem + tm_dk(kdkv & sets_mask), a_ds + k * 8u, desc_at(dm64, b.q + row_off + k * 1024u),
                    idesc_acc, first | k);
-          }
-          if (db_in_tmem) {
-            // dBias^T += dS^T * I: the tensor core sums over the windows of this CTA
-#pragma unroll
-            for (uint32_t k = 0; k < 2; ++k)
-              mma_ts(tmem + tm_db(static_cast<uint32_t>(w)), a_ds + k * 8u, desc_at(dm64, ident + k * 1024u), idesc_acc,
-                     db_started[w] | k | static_cast<uint32_t>(c));
-            if (c == 1) db_started[w] = 1u;
           }
         }
         // the next tile's scores of step w go over this tile's P^T / dS^T of both chunks
@@ -881,7 +881,7 @@ __device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32
   };
 
   Ring kv_ring(NKV), qdo_ring(kNumQdoStages), ds_ring(NDS);
-  uint32_t tile = 0, pt_phase = 0, db_started = 0;
+  uint32_t tile = 0, pt_phase = 0;
   if (!mbar_wait(bar(kbKvReady + 0), 0u, ctx, 60)) return;
   if (!mbar_wait(bar(kbQdoReady + 0), 0u, ctx, 61)) return;
   tc_fence_after();
@@ -916,10 +916,18 @@ __device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32
           mma_ts(tmem + tm_dv(set), a_p + k * 8u, desc_at(dm64, q_base + 2u * kBoxBytes + row_off + k * 1024u),
                  idesc_acc, acc);
           mma_ts(tmem + tm_dk(set), a_ds + k * 8u, desc_at(dm64, q_base + row_off + k * 1024u), idesc_acc, acc);
-          if (db_in_tmem)   // dBias^T += dS^T * I: the tensor core sums over the windows of this CTA
-            mma_ts(tmem + tm_db(w), a_ds + k * 8u, desc_at(dm64, ident + k * 1024u), idesc_acc,
-                   (c | k) ? 1u : db_started);
         }
+      }
+      // dBias^T += dS^T * I: the tensor core sums over the windows of this CTA.  Each step has its
+      // own copy of the identity tile: with one shared copy the products of the step that came
+      // second in a tile produced wrong sums on B200 (measured; the cause is not understood).
+      if (db_in_tmem) {
+#pragma unroll
+        for (uint32_t c = 0; c < 2u; ++c)
+#pragma unroll
+          for (uint32_t k = 0; k < 2u; ++k)
+            mma_ts(tmem + tm_db(w), tmem + w * 128u + kTmDPT + 32u * c + k * 8u, desc_at(dm64, ident + 2048u * w + k * 1024u),
+                   idesc_acc, 1u);
       }
       // the next tile's scores of step w go over this tile's P^T / dS^T
       if (has_next) {
@@ -931,7 +939,6 @@ __device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32
         issue_sdp(w, kn_base, qn_base);
       }
     }
-    db_started = 1u;
     pt_phase ^= 1u;
     // dQ^ += dS K^
     {
@@ -1094,15 +1101,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
     tmem_relinquish();
   }
   // 32 x 32 identity in the layout of a dO chunk (row = query, 64 bytes of columns, 16-byte pieces
-  // XOR-swizzled with the row): B operand of the products that sum dS^T into dBias^T
-  for (uint32_t wi = tid; wi < 512u; wi += kBwdThreads) {
+  // XOR-swizzled with the row), two copies: B operand of the products that sum dS^T into dBias^T
+  for (uint32_t wj = tid; wj < 1024u; wj += kBwdThreads) {
+    const uint32_t wi = wj & 511u;
     const uint32_t row = wi >> 4, piece = (wi >> 2) & 3u, word = wi & 3u;   // word = two columns
     const uint32_t col = ((piece ^ ((row >> 1) & 3u)) << 3) + 2u * word;     // logical column of the low half
     const uint32_t one = Elem<T>::pack(1.f, 0.f) & 0xFFFFu;
     uint32_t v = 0u;
     if (col == row) v = one;
     if (col + 1u == row) v = one << 16;
-    reinterpret_cast<uint32_t*>(smem_raw + p.off_ident)[wi] = v;
+    reinterpret_cast<uint32_t*>(smem_raw + p.off_ident)[wj] = v;
   }
   fence_proxy_async_smem();
   tc_fence_before();

@@ -184,7 +184,7 @@ struct BwdParams {
   uint32_t off_qdo;                  // 2 stages of [Q tile 8 KiB | dO tile 8 KiB]
   uint32_t off_ds;                   // n_ds_bufs tiles of 32 KiB (two 64-query slabs)
   uint32_t off_bm;                   // [warpgroup][stage] of [bias^T 8 KiB | mask^T 8 KiB]
-  uint32_t off_ident;                // 32 x 32 identity (16 bit, MN-major rows of 64 bytes, swizzled)
+  uint32_t off_ident;                // two 32 x 32 identity tiles (16 bit, MN-major rows of 64 bytes, swizzled)
   uint32_t off_rk;                   // n_kv_stages x rows_kv floats: 1 / |k|
   uint32_t off_rowstats;             // 2 stages x (128 lse*log2e, 128 delta) floats
   uint32_t off_ctrl;

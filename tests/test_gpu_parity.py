@@ -77,7 +77,8 @@ def run_case(w, dev, via="autograd", strided=False, variant=0, **kw):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dscale = torch.empty_like(lsx) if st == "tensor" else None
         db = torch.empty_like(bias) if bias is not None else None
-        K._flash_attn_backward(do, q, k, v, lsx, o, lse, dq, dk, dv, dscale, db, bias=bias, mask=mask, scale_type=st)
+        K._flash_attn_backward(do, q, k, v, lsx, o, lse, dq, dk, dv, dscale, db, bias=bias, mask=mask, scale_type=st,
+                               _max_ctas=kw.get("max_ctas", 0))
         got.update(o=o, dq=dq, dk=dk, dv=dv, lse=lse[..., : w.n])
         if dscale is not None:
             got["dscale"] = dscale
@@ -128,6 +129,24 @@ SHAPES = [
 def test_all_arguments_autograd(w, dev):
     got, ref, ins = run_case(w, dev)
     check(w, got, ref, ins)
+
+
+@pytest.mark.parametrize("w,max_ctas", [
+    (Workload("n64_long", batch=16, nw=4, heads=3, window=8, dtype="fp16"), 3),
+    (Workload("n64_long6", batch=5, nw=4, heads=3, window=8, dtype="bf16"), 6),
+    (Workload("n49_long", batch=6, nw=4, heads=2, window=7, dtype="fp16", shift=3), 2),
+    (Workload("n256_long", batch=4, nw=4, heads=2, window=16, dtype="fp16"), 2),
+], ids=lambda x: x.name if hasattr(x, "name") else str(x))
+def test_many_tiles_per_cta(w, max_ctas, dev):
+    """A small grid: every CTA runs through many windows, so whatever it carries from one tile to
+    the next (pipeline phases, the dBias sums it keeps on chip) is exercised; the result must not
+    depend on the grid."""
+    got, ref, ins = run_case(w, dev, via="direct", max_ctas=max_ctas)
+    check(w, got, ref, ins)
+    full, _, _ = run_case(w, dev, via="direct")
+    for key in ("dq", "dk", "dv"):
+        assert torch.equal(got[key], full[key]), key
+    assert orc.rel_err(_f(got["dbias"]), _f(full["dbias"])) < 2e-3
 
 
 @pytest.mark.parametrize("w", SHAPES[:5], ids=lambda w: f"{w.name}-{w.dtype}")
