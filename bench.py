@@ -153,6 +153,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the extra single-GPU configurations")
+    ap.add_argument("--no-graph", action="store_true", help="time the eager step instead of the CUDA-graph replay")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -258,8 +259,27 @@ def main():
     # ------------------------------------------------------------------ the headline workload
     t = make_inputs(w, seed=rank, device=dev)
     step = make_step(w, t)
+    # One GPU: the step (flash_win_attn_v2_func + torch.autograd.grad, four kernels) is captured once
+    # into a CUDA graph and replayed, so that the host's trip through autograd and ctypes is not
+    # what gets timed; the eager number is reported next to it.  More than one GPU: eager (the
+    # sharded step ends in an NCCL all-reduce of the parameter gradients).
+    api = "flash_win_attn_v2_func + torch.autograd.grad"
+    ms_eager = None
+    graphed = None
+    if world == 1 and not args.no_graph:
+        try:
+            from flash_window_attention_v2_b200.graphed import GraphedStep
+            graphed = GraphedStep(t["q"], t["k"], t["v"], t["do"], t["logit_scale"], t["bias"], t["mask"])
+        except Exception as ex:   # capture refused: say so and time the eager step
+            print(f"bench: CUDA graph capture failed ({type(ex).__name__}: {ex}); timing the eager step", file=sys.stderr)
+            graphed = None
     with ClockSampler(local_rank) as clocks:
-        ms_step = time_steps(step, args.steps, max(args.warmup, 3))
+        if graphed is not None:
+            ms_eager = time_steps(step, max(5, args.steps // 2), 3)
+            ms_step = time_steps(graphed.replay, args.steps, max(args.warmup, 3))
+            api += ", captured in a CUDA graph (GraphedStep) and replayed"
+        else:
+            ms_step = time_steps(step, args.steps, max(args.warmup, 3))
         kt = kernel_times(w, t, max(5, args.steps // 2), 3) if rank == 0 or world == 1 else None
     K.check_device_status(dev)
     flops_rank = w.matmul_flops()
@@ -348,12 +368,12 @@ def main():
                 config=dict(workload=w.name, images_per_gpu=w.batch, windows_per_image=w.nw, heads=w.heads, n=w.n,
                             head_dim=w.head_dim, window_heads_per_gpu=w.units,
                             l2="256 MiB buffer rewritten before every timed step",
-                            api="flash_win_attn_v2_func + torch.autograd.grad"),
+                            api=api, eager_ms_per_step=ms_eager),
                 frac_bf16_peak=value / world / peaks["bf16_tflops"],
                 hbm_frac_step=w.algorithmic_bytes() / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
                 roofline=roofline, cpu_baseline=cpu,
                 e2e=dict(value=e2e_val, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=ms_e2e),
-                gpu_launches=((5 if world > 1 else 4) * (args.steps + max(args.warmup, 3))),
+                gpu_launches=((5 if world > 1 else 4) * args.steps),   # inside the timed region of `value`
                 gpu_launches_per_step=(5 if world > 1 else 4), clocks=clocks.summary(), extra=extra)
     print(json.dumps(line), flush=True)
     if world > 1:
