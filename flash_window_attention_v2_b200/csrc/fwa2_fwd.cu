@@ -727,7 +727,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  WaitCtx ctx{&ctrl_words[1], p.status, nullptr};
+  WaitCtx ctx{&ctrl_words[1], p.status, (p.trace.buf != nullptr && p.trace.cap >= 700) ? p.trace.buf + 2ll * p.trace.cap + 500 : nullptr};
 
   if (warp < 4) {
     fwd_softmax_role<T, kPTmem>(p, smem_base, bars, tmem, ctx, scale_tab);
