@@ -157,7 +157,7 @@ BwdPlan make_bwd_plan(int bw, int heads, int n, int n_windows, bool has_bias, bo
   pl.off_mask_t = off;
   if (has_mask) off += align256(static_cast<size_t>(n_windows) * n * pl.table_pitch * 2u);
   pl.off_db = off;
-  if (has_bias) off += align256(static_cast<size_t>(pl.n_bufs) * n * pl.db_pitch * 4u);
+  if (has_bias) off += align256(static_cast<size_t>(pl.n_bufs) * pl.db_pitch * pl.db_pitch * 4u);
   pl.off_dscale = off;
   off += align256(static_cast<size_t>(pl.grid) * 4u);
   pl.total = off;
@@ -350,7 +350,7 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   p.scale = a->logit_scale; p.scale_is_tensor = a->scale_is_tensor;
   p.db_partial = (has_bias && (a->variant & FWA2_BWD_SKIP_DBIAS) == 0) ? reinterpret_cast<float*>(ws + pl.off_db) : nullptr;
   p.db_pitch = pl.db_pitch;
-  p.db_buf_stride = static_cast<long long>(a->n) * pl.db_pitch;
+  p.db_buf_stride = static_cast<long long>(pl.db_pitch) * pl.db_pitch;
   p.dscale_partial = reinterpret_cast<float*>(ws + pl.off_dscale);
   p.BW = a->bw; p.H = a->heads; p.N = a->n; p.nW = has_mask ? a->n_windows : 1;
   p.has_bias = has_bias; p.has_mask = has_mask;

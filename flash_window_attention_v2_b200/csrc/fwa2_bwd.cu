@@ -120,10 +120,8 @@ __device__ __forceinline__ int step_rows(const BwdGeom& g, int i, int w) {
 __device__ __forceinline__ int pair_row_unit(uint32_t r) { return static_cast<int>((r >> 5) & 1u); }
 __device__ __forceinline__ int pair_row_query(uint32_t r) { return static_cast<int>(32u * (r >> 6) + (r & 31u)); }
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
-               : "memory");
+__device__ __forceinline__ void red_add(float* addr, float a) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
 }
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* ptr) {
   uint4 v;
@@ -148,8 +146,8 @@ template <typename T>
 __device__ __forceinline__ void bwd_group(bool has_bias, bool has_mask, const uint32_t (&sv)[8],
                                           const uint32_t (&dpv)[8], uint32_t bias_addr,
                                           uint32_t mask_addr, const float* lse2, const float* delta,
-                                          float scale, bool key_ok, float* db_ptr, bool db_store,
-                                          uint32_t (&pw)[4], uint32_t (&dw)[4]) {
+                                          float scale, bool key_ok, float* db_ptr, int db_pitch,
+                                          bool db_store, uint32_t (&pw)[4], uint32_t (&dw)[4]) {
   uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
   if (has_bias) lds128(bias_addr, wb);
   if (has_mask) lds128(mask_addr, wm);
@@ -174,13 +172,16 @@ __device__ __forceinline__ void bwd_group(bool has_bias, bool has_mask, const ui
     dsv[e] = s0;
     dsv[e + 1] = s1;
   }
+  // The partial is laid out (query, key): the 32 keys of a warp are 128 contiguous bytes of one
+  // query row, so every store / reduction below is one fully used line (a (key, query) layout
+  // with 16-byte vectors per thread touched 32 lines per instruction).
   if (db_ptr != nullptr) {
     if (db_store) {
-      *reinterpret_cast<float4*>(db_ptr) = make_float4(dsv[0], dsv[1], dsv[2], dsv[3]);
-      *reinterpret_cast<float4*>(db_ptr + 4) = make_float4(dsv[4], dsv[5], dsv[6], dsv[7]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) db_ptr[e * db_pitch] = dsv[e];
     } else {
-      red_add_v4(db_ptr, dsv[0], dsv[1], dsv[2], dsv[3]);
-      red_add_v4(db_ptr + 4, dsv[4], dsv[5], dsv[6], dsv[7]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red_add(db_ptr + e * db_pitch, dsv[e]);
     }
   }
 }
@@ -399,8 +400,8 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     kv_next.advance();
     qdo_next.advance();
     // what the preparing warpgroup wrote for this tile and job (row statistics, 1 / |k|) is
-    // visible once its barriers have been seen; both completed long ago
-    if (!mbar_wait(bar(kbKvReady + kv_ring.stage), kv_ring.phase, ctx, 50)) return;
+    // visible once its barrier for the tile has been seen (it completed long ago; the job's K was
+    // normalised by the same threads before they arrived here)
     if (!mbar_wait(bar(kbQdoReady + qdo_ring.stage), qdo_ring.phase, ctx, 51)) return;
     trace_ev(tr, 2);
     // ------------------------------ my share of the current tile ------------------------------
@@ -433,7 +434,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       const long long db_buf = g.pair ? 2ll * blockIdx.x + um : static_cast<long long>(blockIdx.x);
       const int ig0 = g.pair ? 0 : cur.i * kTileRows + static_cast<int>(wg) * kStepCols;
       float* db_row = (p.db_partial != nullptr && key_ok && !g.pair)   // pair mode: summed by the tensor core
-                          ? p.db_partial + db_buf * p.db_buf_stride + static_cast<long long>(jg) * p.db_pitch + ig0
+                          ? p.db_partial + db_buf * p.db_buf_stride + static_cast<long long>(ig0) * p.db_pitch + jg
                           : nullptr;
       const bool db_store = (jt == 0);
       const uint32_t tm_st = tmem + lane_base + step * 128u + kTmST;
@@ -480,7 +481,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           const uint32_t t_s = tm_st + 32u * c, t_d = tm_dpt + 32u * c;
           const float* lse2_c = lse2 + 32 * c;
           const float* delta_c = delta + 32 * c;
-          float* dbp = db_row != nullptr ? db_row + kChunkCols * c : nullptr;
+          float* dbp = db_row != nullptr ? db_row + kChunkCols * c * p.db_pitch : nullptr;
           // four groups of eight queries; the scores of the next group are fetched from tensor
           // memory while the current one is computed (one copy of the group's code: the register
           // moves that rotate the buffers are cheaper than a second copy in the instruction cache)
@@ -497,7 +498,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
             }
             bwd_group<T>(p.has_bias, p.has_mask, sa, da, bias_base + ((gq ^ bias_sw) << 4),
                          mask_base + ((gq ^ mask_sw) << 4), lse2_c + 8u * gq, delta_c + 8u * gq, scale,
-                         key_ok, dbp != nullptr ? dbp + 8u * gq : nullptr, db_store, pw, dw);
+                         key_ok, dbp != nullptr ? dbp + 8u * gq * p.db_pitch : nullptr, p.db_pitch, db_store, pw, dw);
             // P^T and dS^T go back over the first 16 columns of this chunk's own S^T / dP^T columns
             tmem_st4(t_s + 4u * gq, pw);
             tmem_st4(t_d + 4u * gq, dw);
@@ -569,7 +570,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
     tc_fence_after();
     const int jg = static_cast<int>(lt & 63u);
     float* dst = p.db_partial + (2ll * blockIdx.x + (lt >> 6)) * p.db_buf_stride +
-                 static_cast<long long>(jg) * p.db_pitch + kChunkCols * wg;
+                 static_cast<long long>(kChunkCols * wg) * p.db_pitch + jg;
     const bool row_ok = jg < g.N && static_cast<int>(kChunkCols * wg) < p.db_pitch;
     const uint32_t t_db = tmem + lane_base + tm_db(wg);
 #pragma unroll 1
@@ -578,8 +579,8 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       tmem_ld8(t_db + 8u * gq, r);
       tmem_wait_ld();
       if (row_ok) {
-        *reinterpret_cast<uint4*>(dst + 8u * gq) = make_uint4(r[0], r[1], r[2], r[3]);
-        *reinterpret_cast<uint4*>(dst + 8u * gq + 4) = make_uint4(r[4], r[5], r[6], r[7]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dst[(8u * gq + e) * p.db_pitch] = __uint_as_float(r[e]);
       }
     }
     tc_fence_before();

@@ -170,8 +170,8 @@ struct BwdParams {
   long long lse_sbw, lse_sh;
   const void* scale;
   int scale_is_tensor;
-  float* db_partial;          // [n_bufs][N][db_pitch] fp32, transposed: (key, query)
-  long long db_buf_stride;    // N * db_pitch
+  float* db_partial;          // [n_bufs][db_pitch][db_pitch] fp32: (query, key)
+  long long db_buf_stride;    // db_pitch * db_pitch
   int db_pitch;               // N rounded up to 32
   float* dscale_partial;      // [grid]
   int BW, H, N, nW;
@@ -195,7 +195,7 @@ struct BwdParams {
 
 // Second stage of the dBias / dLogitScale reduction.
 struct ReduceParams {
-  const float* db_partial;     // [n_bufs][N][pitch] (key, query)
+  const float* db_partial;     // [n_bufs][pitch][pitch] (query, key)
   long long buf_stride;
   int pitch;
   const float* dscale_partial; // [grid]

@@ -72,17 +72,18 @@ __device__ __forceinline__ int units_of(const ReduceParams& p, int s, int w) {
   return w == 0 ? (count + 1) / 2 : count / 2;
 }
 
-// One block sums an 8 (key) x 32 (query) patch of every partial buffer of its head.  The buffer list
-// is dealt round-robin to kReduceLanes thread rows (threadIdx.y), each of which adds its buffers in
+// One block sums an 8 (query) x 32 (key) patch of every partial buffer of its head; the partials
+// are (query, key) like the result, so there is nothing to transpose.  The buffer list is dealt
+// round-robin to kReduceLanes thread rows (threadIdx.y), each of which adds its buffers in
 // ascending order; the sub-sums are then added in ascending order as well, so the result does not
 // depend on timing.  Many thread rows keep the chain of dependent loads per thread short: the
 // kernel is a few microseconds of latency, not bandwidth.
 constexpr int kReduceLanes = 32;
 template <typename T>
 __global__ void __launch_bounds__(32 * kReduceLanes) reduce_partials_kernel(const ReduceParams p) {
-  __shared__ float part[kReduceLanes][8][33];   // [buffer lane][key][query]
+  __shared__ float part[kReduceLanes][8][33];   // [buffer lane][query][key]
   const int h = blockIdx.z;
-  const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 8;
+  const int j0 = blockIdx.x * 32, i0 = blockIdx.y * 8;
   const int tx = threadIdx.x, ty = threadIdx.y;
   if (p.db_partial != nullptr) {
     float acc[8];
@@ -90,41 +91,33 @@ __global__ void __launch_bounds__(32 * kReduceLanes) reduce_partials_kernel(cons
     for (int r = 0; r < 8; ++r) acc[r] = 0.f;
     const int nw = p.pair ? 2 : 1;
     const int nbuf = p.nslots * nw;
-    const int i = i0 + tx;
+    const int j = j0 + tx;
     for (int b = ty; b < nbuf; b += kReduceLanes) {
       const int s = b / nw, w = b - s * nw;
       if (units_of(p, s, w) == 0) continue;
       const long long buf = static_cast<long long>(s * p.H + h) * nw + w;
       const float* src = p.db_partial + buf * p.buf_stride;
-      if (i < p.N) {
+      if (j < p.N) {
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
-          const int j = j0 + r;
-          if (j < p.N) acc[r] += src[static_cast<long long>(j) * p.pitch + i];
+          const int i = i0 + r;
+          if (i < p.N) acc[r] += src[static_cast<long long>(i) * p.pitch + j];
         }
       }
     }
 #pragma unroll
     for (int r = 0; r < 8; ++r) part[ty][r][tx] = acc[r];
     __syncthreads();
-    // thread (tx, ty < 8) finishes key j0 + ty, query i0 + tx
-    float v = 0.f;
+    // thread (tx, ty < 8) finishes query i0 + ty, key j0 + tx
     if (ty < 8) {
+      float v = 0.f;
 #pragma unroll
       for (int l = 0; l < kReduceLanes; ++l) v += part[l][ty][tx];
-    }
-    __syncthreads();
-    if (ty < 8) part[0][ty][tx] = v;
-    __syncthreads();
-    // write transposed: out[h][query][key], eight consecutive keys per query
-    if (ty < 8) {
-      const int q = ty * 4 + (tx >> 3), kk = tx & 7;   // 32 queries x 8 keys
-      const int qi = i0 + q, kj = j0 + kk;
+      const int qi = i0 + ty, kj = j0 + tx;
       if (qi < p.N && kj < p.N) {
-        const float o = part[0][kk][q];
         const long long idx = (static_cast<long long>(h) * p.N + qi) * p.N + kj;
-        if (p.out_f32 != nullptr) p.out_f32[idx] = o;
-        else if (p.dbias != nullptr) static_cast<uint16_t*>(p.dbias)[idx] = to_raw16<T>(o);
+        if (p.out_f32 != nullptr) p.out_f32[idx] = v;
+        else if (p.dbias != nullptr) static_cast<uint16_t*>(p.dbias)[idx] = to_raw16<T>(v);
       }
     }
   }
