@@ -45,7 +45,10 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks, power and throttle reasons while the timed region runs (read-only).
+
+    NVML through pynvml when it is importable (a query takes well under a millisecond, so that
+    even a timed region of a few milliseconds gets samples), nvidia-smi otherwise."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -53,21 +56,55 @@ class ClockSampler:
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
-        self.samples = []
+        self.samples = []      # (sm_mhz, sm_max_mhz, power_w, hw_slowdown, hw_thermal, sw_thermal, sw_power_cap)
+        self.source = None
         self._stop = threading.Event()
         self._thread = None
 
-    def _run(self):
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if self.gpu < len(ids) and ids[self.gpu].isdigit():
+                return int(ids[self.gpu])
+        return self.gpu
+
+    def _run_nvml(self):
+        import pynvml as nv
+        nv.nvmlInit()
+        h = nv.nvmlDeviceGetHandleByIndex(self._physical_index())
+        mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        bits = dict(hw=0x8, hw_th=0x40, sw_th=0x20, sw_pw=0x4)   # NVML clocks event reason bits
+        self.source = "nvml"
+        while not self._stop.is_set():
+            r = int(get_reasons(h))
+            self.samples.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), mx,
+                                 nv.nvmlDeviceGetPowerUsage(h) / 1000.0,
+                                 bool(r & bits["hw"]), bool(r & bits["hw_th"]), bool(r & bits["sw_th"]),
+                                 bool(r & bits["sw_pw"])))
+            self._stop.wait(0.002)
+
+    def _run_smi(self):
+        self.source = "nvidia-smi"
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
                                       "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
                 parts = [x.strip() for x in out.stdout.strip().split(",")]
                 if len(parts) >= 7:
-                    self.samples.append(parts)
+                    self.samples.append((float(parts[0]), float(parts[1]), float(parts[2]),
+                                         *(x.lower().startswith("active") for x in parts[3:7])))
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(0.05)
+
+    def _run(self):
+        try:
+            self._run_nvml()
+        except Exception:
+            self._run_smi()
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._run, daemon=True)
@@ -81,14 +118,12 @@ class ClockSampler:
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm = sorted(float(s[0]) for s in self.samples)
-        reasons = []
+        sm = sorted(s[0] for s in self.samples)
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for i, nme in enumerate(names):
-            if any(s[3 + i].lower().startswith("active") for s in self.samples):
-                reasons.append(nme)
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.samples[0][1]),
-                "power_w_max": max(float(s[2]) for s in self.samples), "samples": len(sm), "reasons": reasons}
+        reasons = [nme for i, nme in enumerate(names) if any(s[3 + i] for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.samples[0][1],
+                "power_w_max": max(s[2] for s in self.samples), "samples": len(sm), "source": self.source,
+                "reasons": reasons}
 
 
 def cpu_baseline(w, seconds: float = 12.0, sample_images: int | None = None):
@@ -326,7 +361,7 @@ def main():
     # ------------------------------------------------------------------ roofline of the dominant kernel
     # DRAM bytes per launch of the dominant kernel from the ncu captures summarised in profiles/
     # (dram__bytes_read.sum + dram__bytes_write.sum); None for workloads that were not captured
-    ncu_traffic = {"cfg2": 368.3e6, "cfg3": 201.3e6}
+    ncu_traffic = {"cfg2": 368.3e6, "cfg3": 198.7e6}
     bwd_bytes = w.algorithmic_bytes(fwd=False, bwd=True)
     ach = bwd_bytes / (kt["bwd_main"] * 1e-3) / 1e9
     roofline = dict(bound="hbm", kernel="bwd_kernel", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s",
