@@ -296,15 +296,22 @@ def main():
     step = make_step(w, t)
     # One GPU: the step (flash_win_attn_v2_func + torch.autograd.grad, four kernels) is captured once
     # into a CUDA graph and replayed, so that the host's trip through autograd and ctypes is not
-    # what gets timed; the eager number is reported next to it.  More than one GPU: eager (the
-    # sharded step ends in an NCCL all-reduce of the parameter gradients).
+    # what gets timed; the eager number is reported next to it.  More than one GPU: the same local
+    # kernels in a graph, followed (outside the graph) by the NCCL all-reduce of the parameter
+    # gradients and the cast kernel.
     api = "flash_win_attn_v2_func + torch.autograd.grad"
     ms_eager = None
     graphed = None
-    if world == 1 and not args.no_graph:
+    if not args.no_graph:
         try:
-            from flash_window_attention_v2_b200.graphed import GraphedStep
-            graphed = GraphedStep(t["q"], t["k"], t["v"], t["do"], t["logit_scale"], t["bias"], t["mask"])
+            if world == 1:
+                from flash_window_attention_v2_b200.graphed import GraphedStep
+                graphed = GraphedStep(t["q"], t["k"], t["v"], t["do"], t["logit_scale"], t["bias"], t["mask"])
+            else:
+                # the local kernels in a graph; the all-reduce of the parameter gradients and the
+                # cast that follows it stay outside (nothing that waits for a peer is captured)
+                from flash_window_attention_v2_b200.sharded import GraphedShardedStep
+                graphed = GraphedShardedStep(t["q"], t["k"], t["v"], t["do"], t["logit_scale"], t["bias"], t["mask"])
         except Exception as ex:   # capture refused: say so and time the eager step
             print(f"bench: CUDA graph capture failed ({type(ex).__name__}: {ex}); timing the eager step", file=sys.stderr)
             graphed = None
@@ -312,7 +319,9 @@ def main():
         if graphed is not None:
             ms_eager = time_steps(step, max(5, args.steps // 2), 3)
             ms_step = time_steps(graphed.replay, args.steps, max(args.warmup, 3))
-            api += ", captured in a CUDA graph (GraphedStep) and replayed"
+            api = ("flash_win_attn_v2_func + torch.autograd.grad, captured in a CUDA graph (GraphedStep) and replayed"
+                   if world == 1 else
+                   "GraphedShardedStep: local kernels replayed from a CUDA graph, then NCCL all-reduce + cast")
         else:
             ms_step = time_steps(step, args.steps, max(args.warmup, 3))
         kt = kernel_times(w, t, max(5, args.steps // 2), 3) if rank == 0 or world == 1 else None

@@ -117,3 +117,51 @@ class ShardedFlashWindowAttentionV2(torch.autograd.Function):
 def sharded_flash_win_attn_v2_func(q, k, v, logit_scale=None, bias=None, mask=None,
                                    group: Optional[dist.ProcessGroup] = None):
     return ShardedFlashWindowAttentionV2.apply(q, k, v, logit_scale, bias, mask, group)
+
+
+class GraphedShardedStep:
+    """Forward + backward of this rank's windows with the local kernels captured in a CUDA graph.
+
+    The graph holds what needs no other rank (forward, backward, the local fp32 sums of dBias and
+    dLogitScale); the exchange step -- one NCCL all-reduce of `H*N*N + H` floats -- and the final
+    cast run outside it, so that nothing that can block on a peer is inside a capture.
+    Fill `.q .k .v .do` in place, call `replay()`, read `(o, dq, dk, dv, dscale, dbias)`."""
+
+    def __init__(self, q, k, v, do, logit_scale, bias, mask, group: Optional[dist.ProcessGroup] = None):
+        dev = q.device
+        self.group = group
+        self.q, self.k, self.v, self.do = (x.detach().clone() for x in (q, k, v, do))
+        self.logit_scale = logit_scale.detach().clone() if logit_scale is not None else None
+        self.bias = bias.detach().clone() if bias is not None else None
+        self.mask = mask.detach().clone() if mask is not None else None
+        if self.logit_scale is not None:
+            self.scale_type, self._ls = "tensor", self.logit_scale
+        else:
+            self.scale_type = "scalar"
+            self._ls = torch.tensor(1.0 / math.sqrt(q.shape[-1]), device=dev)
+
+        def local():
+            o, lse, ls = CudaBackend.forward(self.q, self.k, self.v, self._ls, self.bias, self.mask, self.scale_type)
+            dq, dk, dv, partial = CudaBackend.backward_partial(self.do, self.q, self.k, self.v, ls, o, lse,
+                                                               self.bias, self.mask, self.scale_type)
+            return o, dq, dk, dv, partial
+
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                local()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.o, self.dq, self.dk, self.dv, self.partial = local()
+
+    def replay(self):
+        self.graph.replay()
+        db = dscale = None
+        if self.partial is not None:
+            if self.group is not None or (dist.is_initialized() and dist.get_world_size() > 1):
+                dist.all_reduce(self.partial, op=dist.ReduceOp.SUM, group=self.group)
+            db, dscale = CudaBackend.finalize(self.partial, self._ls, self.bias, self.scale_type)
+        return self.o, self.dq, self.dk, self.dv, dscale, db

@@ -307,3 +307,34 @@ def test_host_batch_pipeline_matches_direct_calls(dev):
     for e, o in zip(expect, outs):
         for a, b in zip(e, o):
             assert torch.equal(a.cpu(), b)
+
+
+def test_graph_replay_matches_eager_calls(dev):
+    """The CUDA-graph wrappers replay exactly what the eager calls compute, also after their static
+    inputs have been overwritten with a new batch."""
+    from flash_window_attention_v2_b200 import flash_win_attn_v2_func
+    from flash_window_attention_v2_b200.graphed import GraphedStep
+    from flash_window_attention_v2_b200.sharded import GraphedShardedStep
+    w = Workload("n64", batch=4, nw=4, heads=3, window=8, dtype="bf16")
+    t0, t1 = make_inputs(w, seed=0, device=dev), make_inputs(w, seed=1, device=dev)
+
+    def eager(t):
+        q, k, v = (t[x].detach().requires_grad_(True) for x in ("q", "k", "v"))
+        ls, bias = t["logit_scale"].detach().requires_grad_(True), t["bias"].detach().requires_grad_(True)
+        o = flash_win_attn_v2_func(q, k, v, ls, bias, t["mask"])
+        return [o.detach()] + list(torch.autograd.grad(o, (q, k, v, ls, bias), t["do"]))
+
+    g = GraphedStep(t0["q"], t0["k"], t0["v"], t0["do"], t0["logit_scale"], t0["bias"], t0["mask"])
+    gs = GraphedShardedStep(t0["q"], t0["k"], t0["v"], t0["do"], t0["logit_scale"], t0["bias"], t0["mask"])
+    for t in (t0, t1):
+        for obj in (g, gs):
+            with torch.no_grad():
+                obj.q.copy_(t["q"]); obj.k.copy_(t["k"]); obj.v.copy_(t["v"]); obj.do.copy_(t["do"])
+                obj.logit_scale.copy_(t["logit_scale"]); obj.bias.copy_(t["bias"]); obj.mask.copy_(t["mask"])
+        want = eager(t)
+        got = g.replay()
+        for a, b in zip(want, got):
+            assert torch.equal(a, b)
+        o, dq, dk, dv, dscale, db = gs.replay()
+        for a, b in zip(want, (o, dq, dk, dv, dscale, db)):
+            assert torch.equal(a, b)
