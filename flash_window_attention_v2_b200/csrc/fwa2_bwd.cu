@@ -604,59 +604,53 @@ __device__ void bwd_prepare_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
   float* rk_arr = reinterpret_cast<float*>(smem_ptr + p.off_rk);
   float* rowstats = reinterpret_cast<float*>(smem_ptr + p.off_rowstats);
 
-  struct ORow {
-    uint4 v[4];
-    float lse;
-    bool ok;
-  };
-  auto load_o_row = [&](const TileIt& it, ORow& dst) {
-    const int m = g.pair ? pair_row_unit(lt) : 0;
-    const int bw = bwd_bw(p, g, it.t, m);
-    const int ig = g.pair ? pair_row_query(lt) : it.i * kTileRows + static_cast<int>(lt);
-    dst.ok = bw < p.BW && ig < g.N;
-    if (dst.ok) {
-      const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) dst.v[ch] = ldg_nc_v4(orow + ch * 8);
-      dst.lse = __ldg(p.lse + bw * p.lse_sbw + g.h * p.lse_sh + ig);
-    }
-  };
-
   TileIt it{0, 0, 0};
   Ring kv(p.n_kv_stages), qdo(kNumQdoStages);
   bool new_job = true;
-  ORow o_cur{}, o_next{};
-  load_o_row(it, o_cur);
 #pragma unroll 1
   while (true) {
-    TileIt nx = it;
-    const bool has_next = tile_next(g, nx);
-    if (has_next) load_o_row(nx, o_next);
+    // the O row and lse of my query: fetched first, used last (the normalisations hide most of the
+    // latency; this warpgroup has slack, and one copy of the loads keeps its code small)
+    const int m = g.pair ? pair_row_unit(lt) : 0;
+    const int bw = bwd_bw(p, g, it.t, m);
+    const int ig = g.pair ? pair_row_query(lt) : it.i * kTileRows + static_cast<int>(lt);
+    const bool row_ok = bw < p.BW && ig < g.N;
+    uint4 o_row[4];
+    float lse = 0.f;
+    if (row_ok) {
+      const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) o_row[ch] = ldg_nc_v4(orow + ch * 8);
+      lse = __ldg(p.lse + bw * p.lse_sbw + g.h * p.lse_sh + ig);
+    }
 
-    if (new_job) {
-      const uint32_t kvs = kv.stage;
-      const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
-      if (!mbar_wait(bar(kbKvFull + kvs), kv.phase, ctx, 80)) return;
+    // K rows of a new job, then my Q row: the same normalisation code for both
+    const uint32_t qs = qdo.stage;
+    const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
 #pragma unroll 1
-      for (uint32_t rr = lt; rr < static_cast<uint32_t>(p.rows_kv); rr += 128u)
-        rk_arr[kvs * p.rows_kv + rr] = normalise_row<T>(k_base, rr);
+    for (int what = new_job ? 0 : 1; what < 2; ++what) {
+      const uint32_t kvs = kv.stage;
+      const uint32_t base = what == 0 ? smem_base + p.off_kv + kvs * p.kv_stage_bytes : q_base;
+      const uint32_t rows = what == 0 ? static_cast<uint32_t>(p.rows_kv) : static_cast<uint32_t>(kTileRows);
+      if (!mbar_wait(bar(what == 0 ? kbKvFull + kvs : kbQdoFull + qs), what == 0 ? kv.phase : qdo.phase, ctx, 80 + what))
+        return;
+#pragma unroll 1
+      for (uint32_t rr = lt; rr < rows; rr += 128u) {
+        const float rn = normalise_row<T>(base, rr);
+        if (what == 0) rk_arr[kvs * p.rows_kv + rr] = rn;
+      }
       fence_proxy_async_smem();
-      mbar_arrive(bar(kbKvReady + kvs));
+      if (what == 0) mbar_arrive(bar(kbKvReady + kvs));
     }
     {
-      const uint32_t qs = qdo.stage;
-      const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
-      if (!mbar_wait(bar(kbQdoFull + qs), qdo.phase, ctx, 81)) return;
-      normalise_row<T>(q_base, lt);
-      fence_proxy_async_smem();
       float l2 = INFINITY, dl = 0.f;
-      if (o_cur.ok) {
+      if (row_ok) {
         float dlp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t wd[4];
           lds128(q_base + 2u * kBoxBytes + sw64_offset(lt, ch), wd);
-          const uint32_t wo[4] = {o_cur.v[ch].x, o_cur.v[ch].y, o_cur.v[ch].z, o_cur.v[ch].w};
+          const uint32_t wo[4] = {o_row[ch].x, o_row[ch].y, o_row[ch].z, o_row[ch].w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             dlp[ch] = fmaf(Elem<T>::lo(wd[i]), Elem<T>::lo(wo[i]), dlp[ch]);
@@ -664,18 +658,17 @@ __device__ void bwd_prepare_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           }
         }
         dl = (dlp[0] + dlp[1]) + (dlp[2] + dlp[3]);
-        l2 = (o_cur.lse == -INFINITY) ? INFINITY : o_cur.lse * kLog2e;
+        l2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
       }
       rowstats[qs * 256u + lt] = l2;
       rowstats[qs * 256u + 128u + lt] = dl;
       mbar_arrive(bar(kbQdoReady + qs));
     }
-    if (!has_next) break;
-    new_job = nx.t != it.t;
+    const int t_before = it.t;
+    if (!tile_next(g, it)) break;
+    new_job = it.t != t_before;
     if (new_job) kv.advance();
     qdo.advance();
-    it = nx;
-    o_cur = o_next;
   }
 }
 
@@ -886,8 +879,8 @@ __device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32
   if (!mbar_wait(bar(kbKvReady + 0), 0u, ctx, 60)) return;
   if (!mbar_wait(bar(kbQdoReady + 0), 0u, ctx, 61)) return;
   tc_fence_after();
-  issue_sdp(0u, smem_base + p.off_kv, smem_base + p.off_qdo);
-  issue_sdp(1u, smem_base + p.off_kv, smem_base + p.off_qdo);
+#pragma unroll 1
+  for (uint32_t w = 0; w < 2u; ++w) issue_sdp(w, smem_base + p.off_kv, smem_base + p.off_qdo);
 
 #pragma unroll 1
   for (int t = 0; t < g.njobs; ++t, ++tile) {
@@ -907,7 +900,7 @@ __device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32
     for (uint32_t w = 0; w < 2u; ++w) {
       if (!mbar_wait(bar(kbPtFull + 2 * static_cast<int>(w)), pt_phase, ctx, 64)) return;
       tc_fence_after();
-#pragma unroll
+#pragma unroll 1
       for (uint32_t c = 0; c < 2u; ++c) {
         const uint32_t row_off = (w * kStepCols + c * kChunkCols) * kRowBytes;
         const uint32_t a_p = tmem + w * 128u + kTmST + 32u * c, a_ds = tmem + w * 128u + kTmDPT + 32u * c;
@@ -923,12 +916,10 @@ __device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32
       // own copy of the identity tile: with one shared copy the products of the step that came
       // second in a tile produced wrong sums on B200 (measured; the cause is not understood).
       if (db_in_tmem) {
-#pragma unroll
-        for (uint32_t c = 0; c < 2u; ++c)
-#pragma unroll
-          for (uint32_t k = 0; k < 2u; ++k)
-            mma_ts(tmem + tm_db(w), tmem + w * 128u + kTmDPT + 32u * c + k * 8u, desc_at(dm64, ident + 2048u * w + k * 1024u),
-                   idesc_acc, 1u);
+#pragma unroll 1
+        for (uint32_t ck = 0; ck < 4u; ++ck)   // chunk ck / 2, k-step ck % 2
+          mma_ts(tmem + tm_db(w), tmem + w * 128u + kTmDPT + 32u * (ck >> 1) + (ck & 1u) * 8u,
+                 desc_at(dm64, ident + 2048u * w + (ck & 1u) * 1024u), idesc_acc, 1u);
       }
       // the next tile's scores of step w go over this tile's P^T / dS^T
       if (has_next) {
@@ -1174,6 +1165,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
         (smid + 1000) | (static_cast<unsigned long long>(clock64() - c_start) << 16);
   }
 #endif
+  if (tid == 0) report_abort(ctrl_words[1], p.status);
   if (ctrl_words[1]) {
     __nanosleep(20000);
     __syncthreads();

@@ -738,6 +738,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_consta
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) report_abort(ctrl_words[1], p.status);
   if (abort_flag) {
     // A wait ran out somewhere: give copies that may still be in flight time to land before the
     // shared memory is handed back.

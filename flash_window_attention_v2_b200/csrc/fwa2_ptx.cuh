@@ -129,20 +129,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 #endif
   if (mbar_try_wait(bar, parity)) return true;
 #if FWA2_WAIT_INLINE
+  // Inline polling loop, kept short (it exists at every wait site of an instruction-cache-bound
+  // kernel): on expiry only the CTA's abort word is set, to (site << 8 | kind); the kernel copies
+  // it into the caller's status word at its end (report_abort()).
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3Fu) == 0) {
+    if ((++spins & 0xFFu) == 0) {
       if (*ctx.abort_flag) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
-        *ctx.abort_flag = 1u;
-        if (ctx.status != nullptr) {
-          if (atomicCAS(&ctx.status->code, 0u, (site << 8) | kStatusTimeout) == 0u) {
-            ctx.status->block = blockIdx.x;
-            ctx.status->detail = parity;
-          }
-        }
+        *ctx.abort_flag = (site << 8) | kStatusTimeout;
         return false;
       }
     }
@@ -150,6 +147,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 #else
   return mbar_wait_slow(bar, parity, ctx.abort_flag, ctx.status, site);
 #endif
+}
+
+// End of kernel, one thread: a wait that ran out left (site << 8 | kind) in the CTA's abort word;
+// the first CTA to report wins the caller's status word.
+__device__ __forceinline__ void report_abort(uint32_t abort_word, DeviceStatus* status) {
+  if (abort_word != 0u && status != nullptr) {
+    const uint32_t code = (abort_word >> 8) != 0u ? abort_word : ((99u << 8) | kStatusTimeout);
+    if (atomicCAS(&status->code, 0u, code) == 0u) {
+      status->block = blockIdx.x;
+      status->detail = 0u;
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
