@@ -86,29 +86,25 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
   uint32_t tt = 0, pvc = 0;
   Ring kv_ring(p.n_kv_stages), s_ring(sh.pair ? 1u : 2u), bm_ring(p.n_bm_stages);
   TraceCursor tr = (tid == 0) ? trace_begin(p.trace, 0) : TraceCursor{nullptr, 0};
-  // ---- K rows of a job: normalised in place ----
-  auto prologue_kv = [&](const Ring& r) -> bool {
-    const uint32_t kvs = r.stage;
-    const uint32_t kv_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
-    if (!mbar_wait(bar(kBarKvFull + kvs), r.phase, ctx, 10)) return false;
-    trace_ev(tr, 1);
-    for (uint32_t rr = tid; rr < static_cast<uint32_t>(sh.rows_kv); rr += 128u)
-      normalise_row<T>(kv_base, rr);
-    fence_proxy_async_smem();
-    mbar_arrive(bar(kBarKvReady + kvs));
-    trace_ev(tr, 2);
-    return true;
-  };
-  // ---- my Q row of a tile: normalised in place ----
-  auto prologue_q = [&](uint32_t ttn) -> bool {
-    const uint32_t qs = ttn & 1u;
-    const uint32_t q_base = smem_base + p.off_q + qs * (2u * kBoxBytes);
-    if (!mbar_wait(bar(kBarQFull + qs), (ttn >> 1) & 1u, ctx, 11)) return false;
-    trace_ev(tr, 3);
-    normalise_row<T>(q_base, tid);
-    fence_proxy_async_smem();
-    mbar_arrive(bar(kBarQReady + qs));
-    trace_ev(tr, 4);
+  // ---- K rows of a job (what = 0) and my Q row of a tile (what = 1), normalised in place.  One
+  // loop for both, so that the normalisation code exists once per call site. ----
+  auto prepare = [&](bool with_kv, const Ring& r, uint32_t ttn) -> bool {
+#pragma unroll 1
+    for (int what = with_kv ? 0 : 1; what < 2; ++what) {
+      const uint32_t kvs = r.stage, qs = ttn & 1u;
+      const uint32_t base = what == 0 ? smem_base + p.off_kv + kvs * p.kv_stage_bytes
+                                      : smem_base + p.off_q + qs * (2u * kBoxBytes);
+      const uint32_t rows = what == 0 ? static_cast<uint32_t>(sh.rows_kv) : static_cast<uint32_t>(kTileRows);
+      if (!mbar_wait(bar(what == 0 ? kBarKvFull + kvs : kBarQFull + qs), what == 0 ? r.phase : ((ttn >> 1) & 1u),
+                     ctx, 10 + what))
+        return false;
+      trace_ev(tr, 1 + 2 * what);
+#pragma unroll 1
+      for (uint32_t rr = tid; rr < rows; rr += 128u) normalise_row<T>(base, rr);
+      fence_proxy_async_smem();
+      mbar_arrive(bar(what == 0 ? kBarKvReady + kvs : kBarQReady + qs));
+      trace_ev(tr, 2 + 2 * what);
+    }
     return true;
   };
   // The prologue of the NEXT tile runs before the epilogue of the current one, so that the MMA
@@ -121,14 +117,13 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
     const int bw = unit / sh.H, h = unit - bw * sh.H;
     const float scale = scale_tab[h];
 
-    if (!kv_ahead) {
-      if (!prologue_kv(kv_ring)) return;
-    }
+    // (ahead: already done at the end of the previous tile)
+    const bool need_kv = !kv_ahead;
     kv_ahead = false;
 
     for (int mt = 0; mt < sh.MT; ++mt, ++tt) {
       if (!q_ahead) {
-        if (!prologue_q(tt)) return;
+        if (!prepare(need_kv && mt == 0, kv_ring, tt)) return;
       }
       q_ahead = false;
 
@@ -412,16 +407,16 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
 
 #endif
       // ---- prologue of the next tile (and job) ----
-      if (mt + 1 < sh.MT) {
-        if (!prologue_q(tt + 1)) return;
-        q_ahead = true;
-      } else if (job + static_cast<int>(gridDim.x) < p.n_jobs && p.n_kv_stages >= 2) {
-        Ring nx = kv_ring;
-        nx.advance();
-        if (!prologue_kv(nx)) return;
-        kv_ahead = true;
-        if (!prologue_q(tt + 1)) return;
-        q_ahead = true;
+      {
+        const bool next_tile = mt + 1 < sh.MT;
+        const bool next_job = !next_tile && job + static_cast<int>(gridDim.x) < p.n_jobs && p.n_kv_stages >= 2;
+        if (next_tile || next_job) {
+          Ring nx = kv_ring;
+          if (next_job) nx.advance();
+          if (!prepare(next_job, nx, tt + 1)) return;
+          q_ahead = true;
+          kv_ahead = next_job;
+        }
       }
 
       // ---- last P*V of the tile, then the epilogue ----
