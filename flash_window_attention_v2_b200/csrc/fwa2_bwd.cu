@@ -142,36 +142,27 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* ptr) {
 // the 32 queries of a chunk): these kernels are bound by instruction fetch, and the loop body has
 // to stay resident in the instruction cache next to the other roles' code.
 // ------------------------------------------------------------------------------------------------
-template <typename T, int kW>   // kW queries: 8 or 16 (16: twice the independent work per trip)
-__device__ __forceinline__ void bwd_group(bool has_bias, bool has_mask, const uint32_t (&sv)[kW],
-                                          const uint32_t (&dpv)[kW], uint32_t bias_row_addr, uint32_t bias_sw,
-                                          uint32_t mask_row_addr, uint32_t mask_sw, uint32_t piece0,
-                                          const float* lse2, const float* delta, float scale, bool key_ok,
-                                          float* db_ptr, int db_pitch, bool db_store,
-                                          uint32_t (&pw)[kW / 2], uint32_t (&dw)[kW / 2]) {
-  constexpr int kP = kW / 8;   // 16-byte pieces of a table row
-  uint32_t wb[kP][4], wm[kP][4];
-  float l8[kW], d8[kW];
+template <typename T>
+__device__ __forceinline__ void bwd_group(bool has_bias, bool has_mask, const uint32_t (&sv)[8],
+                                          const uint32_t (&dpv)[8], uint32_t bias_addr,
+                                          uint32_t mask_addr, const float* lse2, const float* delta,
+                                          float scale, bool key_ok, float* db_ptr, int db_pitch,
+                                          bool db_store, uint32_t (&pw)[4], uint32_t (&dw)[4]) {
+  uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
+  if (has_bias) lds128(bias_addr, wb);
+  if (has_mask) lds128(mask_addr, wm);
+  const float4 la = *reinterpret_cast<const float4*>(lse2);
+  const float4 lb = *reinterpret_cast<const float4*>(lse2 + 4);
+  const float4 da = *reinterpret_cast<const float4*>(delta);
+  const float4 db = *reinterpret_cast<const float4*>(delta + 4);
+  const float l8[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+  const float d8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+  float dsv[8];
 #pragma unroll
-  for (int h = 0; h < kP; ++h) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { wb[h][i] = 0u; wm[h][i] = 0u; }
-    if (has_bias) lds128(bias_row_addr + (((piece0 + h) ^ bias_sw) << 4), wb[h]);
-    if (has_mask) lds128(mask_row_addr + (((piece0 + h) ^ mask_sw) << 4), wm[h]);
-#pragma unroll
-    for (int v = 0; v < 2; ++v) {
-      const float4 lv = *reinterpret_cast<const float4*>(lse2 + 8 * h + 4 * v);
-      const float4 dv = *reinterpret_cast<const float4*>(delta + 8 * h + 4 * v);
-      l8[8 * h + 4 * v + 0] = lv.x; l8[8 * h + 4 * v + 1] = lv.y; l8[8 * h + 4 * v + 2] = lv.z; l8[8 * h + 4 * v + 3] = lv.w;
-      d8[8 * h + 4 * v + 0] = dv.x; d8[8 * h + 4 * v + 1] = dv.y; d8[8 * h + 4 * v + 2] = dv.z; d8[8 * h + 4 * v + 3] = dv.w;
-    }
-  }
-  float dsv[kW];
-#pragma unroll
-  for (int e2 = 0; e2 < kW / 2; ++e2) {
-    const int e = 2 * e2, h = e2 >> 2, i = e2 & 3;
-    const float x0 = fmaf(__uint_as_float(sv[e]), scale, Elem<T>::lo(wb[h][i])) + Elem<T>::lo(wm[h][i]);
-    const float x1 = fmaf(__uint_as_float(sv[e + 1]), scale, Elem<T>::hi(wb[h][i])) + Elem<T>::hi(wm[h][i]);
+  for (int e2 = 0; e2 < 4; ++e2) {
+    const int e = 2 * e2;
+    const float x0 = fmaf(__uint_as_float(sv[e]), scale, Elem<T>::lo(wb[e2])) + Elem<T>::lo(wm[e2]);
+    const float x1 = fmaf(__uint_as_float(sv[e + 1]), scale, Elem<T>::hi(wb[e2])) + Elem<T>::hi(wm[e2]);
     const float p0 = ex2f(fmaf(x0, kLog2e, -l8[e]));
     const float p1 = ex2f(fmaf(x1, kLog2e, -l8[e + 1]));
     const float s0 = p0 * (__uint_as_float(dpv[e]) - d8[e]);
@@ -187,10 +178,10 @@ __device__ __forceinline__ void bwd_group(bool has_bias, bool has_mask, const ui
   if (db_ptr != nullptr) {
     if (db_store) {
 #pragma unroll
-      for (int e = 0; e < kW; ++e) db_ptr[e * db_pitch] = dsv[e];
+      for (int e = 0; e < 8; ++e) db_ptr[e * db_pitch] = dsv[e];
     } else {
 #pragma unroll
-      for (int e = 0; e < kW; ++e) red_add(db_ptr + e * db_pitch, dsv[e]);
+      for (int e = 0; e < 8; ++e) red_add(db_ptr + e * db_pitch, dsv[e]);
     }
   }
 }
@@ -491,34 +482,29 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           const float* lse2_c = lse2 + 32 * c;
           const float* delta_c = delta + 32 * c;
           float* dbp = db_row != nullptr ? db_row + kChunkCols * c * p.db_pitch : nullptr;
-          // two groups of sixteen queries; the scores of the second group are fetched from tensor
-          // memory while the first is computed (one copy of the group's code: the register moves
-          // that rotate the buffers are cheaper than a second copy in the instruction cache)
-          constexpr int kW = 16;
-          uint32_t sa[kW], da[kW], sb[kW], db8[kW];
-          tmem_ld16(t_s, sa);
-          tmem_ld16(t_d, da);
+          // four groups of eight queries; the scores of the next group are fetched from tensor
+          // memory while the current one is computed (one copy of the group's code: the register
+          // moves that rotate the buffers are cheaper than a second copy in the instruction cache)
+          uint32_t sa[8], da[8], sb[8], db8[8];
+          tmem_ld8(t_s, sa);
+          tmem_ld8(t_d, da);
 #pragma unroll 1
-          for (uint32_t gq = 0; gq < 2u; ++gq) {
-            uint32_t pw[kW / 2], dw[kW / 2];
+          for (uint32_t gq = 0; gq < 4u; ++gq) {
+            uint32_t pw[4], dw[4];
             tmem_wait_ld();
-            if (gq + 1u < 2u) {
-              tmem_ld16(t_s + kW * (gq + 1u), sb);
-              tmem_ld16(t_d + kW * (gq + 1u), db8);
+            if (gq + 1u < 4u) {
+              tmem_ld8(t_s + 8u * (gq + 1u), sb);
+              tmem_ld8(t_d + 8u * (gq + 1u), db8);
             }
-            bwd_group<T, kW>(p.has_bias, p.has_mask, sa, da, bias_base, bias_sw, mask_base, mask_sw, 2u * gq,
-                             lse2_c + kW * gq, delta_c + kW * gq, scale, key_ok,
-                             dbp != nullptr ? dbp + kW * gq * p.db_pitch : nullptr, p.db_pitch, db_store, pw, dw);
+            bwd_group<T>(p.has_bias, p.has_mask, sa, da, bias_base + ((gq ^ bias_sw) << 4),
+                         mask_base + ((gq ^ mask_sw) << 4), lse2_c + 8u * gq, delta_c + 8u * gq, scale,
+                         key_ok, dbp != nullptr ? dbp + 8u * gq * p.db_pitch : nullptr, p.db_pitch, db_store, pw, dw);
             // P^T and dS^T go back over the first 16 columns of this chunk's own S^T / dP^T columns
-            tmem_st8(t_s + 8u * gq, pw);
-            tmem_st8(t_d + 8u * gq, dw);
+            tmem_st4(t_s + 4u * gq, pw);
+            tmem_st4(t_d + 4u * gq, dw);
+            sts128(ds_base + (((4u * c + gq) ^ ds_sw) << 4), dw);
 #pragma unroll
-            for (uint32_t h = 0; h < 2u; ++h) {
-              const uint32_t w4[4] = {dw[4 * h], dw[4 * h + 1], dw[4 * h + 2], dw[4 * h + 3]};
-              sts128(ds_base + (((4u * c + 2u * gq + h) ^ ds_sw) << 4), w4);
-            }
-#pragma unroll
-            for (int i = 0; i < kW; ++i) {
+            for (int i = 0; i < 8; ++i) {
               sa[i] = sb[i];
               da[i] = db8[i];
             }
