@@ -632,7 +632,7 @@ __device__ void bwd_prepare_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
       const uint32_t kvs = kv.stage;
       const uint32_t base = what == 0 ? smem_base + p.off_kv + kvs * p.kv_stage_bytes : q_base;
       const uint32_t rows = what == 0 ? static_cast<uint32_t>(p.rows_kv) : static_cast<uint32_t>(kTileRows);
-      if (!mbar_wait(bar(what == 0 ? kbKvFull + kvs : kbQdoFull + qs), what == 0 ? kv.phase : qdo.phase, ctx, 80 + what))
+      if (!mbar_wait<true>(bar(what == 0 ? kbKvFull + kvs : kbQdoFull + qs), what == 0 ? kv.phase : qdo.phase, ctx, 80 + what))
         return;
 #pragma unroll 1
       for (uint32_t rr = lt; rr < rows; rr += 128u) {
@@ -969,7 +969,7 @@ __device__ void bwd_load_main(const BwdParams& p, uint32_t smem_base, uint32_t b
   while (true) {
     if (new_job) {
       const uint32_t kvs = kv.stage;
-      if (!mbar_wait(bar(kbKvFree + kvs), kv.phase ^ 1u, ctx, 70)) return;
+      if (!mbar_wait<true>(bar(kbKvFree + kvs), kv.phase ^ 1u, ctx, 70)) return;
       const uint32_t k_base = smem_base + p.off_kv + kvs * p.kv_stage_bytes;
       const uint32_t v_base = k_base + static_cast<uint32_t>(p.rows_kv) * kRowBytes;
       const uint32_t full = bar(kbKvFull + kvs);
@@ -985,7 +985,7 @@ __device__ void bwd_load_main(const BwdParams& p, uint32_t smem_base, uint32_t b
     }
     {
       const uint32_t qs = qdo.stage;
-      if (!mbar_wait(bar(kbQdoFree + qs), qdo.phase ^ 1u, ctx, 71)) return;
+      if (!mbar_wait<true>(bar(kbQdoFree + qs), qdo.phase ^ 1u, ctx, 71)) return;
       const uint32_t q_base = smem_base + p.off_qdo + qs * kQdoStageBytes;
       const uint32_t full = bar(kbQdoFull + qs);
       mbar_arrive_expect_tx(full, kQdoStageBytes);
@@ -1028,7 +1028,7 @@ __device__ void bwd_load_tables(const BwdParams& p, uint32_t smem_base, uint32_t
 #pragma unroll 1
     for (int c = 0; c < nchunks; ++c) {
       const uint32_t st = bm.stage;
-      if (!mbar_wait(bar(kbBmFree + 2 * w + st), bm.phase ^ 1u, ctx, 72)) return;
+      if (!mbar_wait<true>(bar(kbBmFree + 2 * w + st), bm.phase ^ 1u, ctx, 72)) return;
       const uint32_t base = smem_base + p.off_bm + (w * NBM + st) * (2u * kTableTileBytes);
       const uint32_t full = bar(kbBmFull + 2 * w + st);
       mbar_arrive_expect_tx(full, tx_bytes);

@@ -111,6 +111,10 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 #ifndef FWA2_WAIT_INLINE
 #define FWA2_WAIT_INLINE 0
 #endif
+// kRelaxed: for roles that run ahead of their consumers (producers, preparing warps) -- the polling
+// loop backs off with nanosleep, so that it does not take issue slots from the warps that do the
+// arithmetic on the same scheduler.
+template <bool kRelaxed = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           uint32_t site) {
 #if defined(FWA2_TRACE) && FWA2_TRACE
@@ -136,6 +140,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (kRelaxed) __nanosleep(200);
     if ((++spins & 0xFFu) == 0) {
       if (*ctx.abort_flag) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
