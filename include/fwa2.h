@@ -138,6 +138,23 @@ int fwa2_backward(const fwa2_bwd_args* args, void* stream);
 int fwa2_finalize_grads(const float* partial, int32_t dtype, int32_t heads, int32_t n,
                         const void* logit_scale, void* dbias, void* dscale, void* stream);
 
+/* The step in front of the operator in Swin-V2 (swin_transformer_v2.py:283-287), fused into one
+ * kernel:  bias[h, i, j] = 16 * sigmoid(table[index[i, j], h]).
+ * table: (rows, heads), fp32 when table_is_f32 else `dtype`; index: (n, n) int32 with values in
+ * [0, rows); bias: (heads, n, n) contiguous, `dtype`. */
+int fwa2_cpb_bias_forward(const void* table, int32_t table_is_f32, const int32_t* index, int32_t dtype,
+                          int32_t n, int32_t heads, int32_t rows, void* bias, void* stream);
+
+/* Its backward, fed with the fp32 window-summed dBias that fwa2_backward leaves in `partial_out`
+ * (so the gradient never passes through a 16-bit (heads, n, n) tensor):
+ *   dtable[r, h] = 16 s (1 - s) * sum_{index[i, j] = r} dbias[h, i, j],  s = sigmoid(table[r, h]).
+ * row_offsets (rows + 1) / positions (n * n): the inverse of `index` in CSR form (positions of
+ * row r are positions[row_offsets[r] .. row_offsets[r + 1]), flat i * n + j, ascending); the
+ * summation order is fixed, the result bitwise reproducible.  dtable: (rows, heads) fp32. */
+int fwa2_cpb_bias_backward(const float* dbias_f32, const void* table, int32_t table_is_f32, int32_t dtype,
+                           const int32_t* row_offsets, const int32_t* positions, int32_t n, int32_t heads,
+                           int32_t rows, float* dtable_f32, void* stream);
+
 /* Backward pass that allocates nothing and takes no workspace.  (No counterpart in the reference
  * project, which allocates its fp32 accumulators with torch on every call.)
  *
