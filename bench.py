@@ -402,6 +402,32 @@ def main():
             del tx
             torch.cuda.empty_cache()
 
+    # the bias-preparation step in front of the operator (not part of the headline metric): fused
+    # kernels against the reference's own torch expression, both on this GPU
+    if not args.no_extra and world == 1:
+        try:
+            from flash_window_attention_v2_b200.cpb_bias import cpb_bias_backward, cpb_bias_forward
+            from oracle.window_attention_oracle import relative_position_index
+            side = int(round(math.sqrt(w.n)))
+            if side * side == w.n:
+                idx = torch.from_numpy(relative_position_index(side, side)).to(dev)
+                tab = torch.randn((2 * side - 1) ** 2, w.heads, device=dev).to(t["q"].dtype)
+                dbf = torch.randn(w.heads, w.n, w.n, device=dev)
+
+                def torch_expr():
+                    tt = tab.detach().requires_grad_(True)
+                    b = 16 * torch.sigmoid(tt[idx.view(-1)].view(w.n, w.n, -1).permute(2, 0, 1).contiguous())
+                    return torch.autograd.grad(b, tt, dbf.to(b.dtype))
+
+                def fused():
+                    cpb_bias_forward(tab, idx, tab.dtype)
+                    return cpb_bias_backward(dbf, tab, idx, tab.dtype)
+
+                extra["cpb_bias_step"] = dict(n=w.n, heads=w.heads, fused_fwd_bwd_ms=time_steps(fused, 10, 3),
+                                              torch_expression_fwd_bwd_ms=time_steps(torch_expr, 10, 3))
+        except Exception as ex:   # an extra: never let it take the headline line down
+            extra["cpb_bias_step"] = dict(error=f"{type(ex).__name__}: {ex}")
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(w)
