@@ -126,8 +126,18 @@ class ClockSampler:
                 "reasons": reasons}
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every core it may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+
+
 def cpu_baseline(w, seconds: float = 12.0, sample_images: int | None = None):
     """Times oracle/classic_cpu.py (fp32, all host threads) on `sample_images` images of `w`."""
+    use_all_host_threads()
     from oracle import classic_cpu
     if sample_images is None:
         # aim at roughly a second per pass: the classic path materialises (BW, H, N, N) fp32
@@ -154,6 +164,7 @@ def run_reference(args, w, rank):
     """The reference arm: its classic path on the host cores; rank 0 only."""
     if rank != 0:
         return
+    use_all_host_threads()
     per_image = w.nw * w.heads * w.n * w.n * 4
     sample_images = max(1, min(w.batch, int(1.5e8 // per_image)))
     from oracle import classic_cpu
