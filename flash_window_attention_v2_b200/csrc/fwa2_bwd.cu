@@ -73,11 +73,14 @@ struct BwdGeom {
   int N, H, pair, KB, MT, h, slot, nslots, count, njobs;
 };
 
+// kPair is a template parameter of the kernel: each launch runs code specialised for its mode, so
+// the instruction cache holds none of the other mode's branches between the hot instructions.
+template <bool kPair>
 __device__ __forceinline__ BwdGeom bwd_geom(const BwdParams& p) {
   BwdGeom g;
   g.N = p.N;
   g.H = p.H;
-  g.pair = p.pair_mode;
+  g.pair = kPair ? 1 : 0;
   g.KB = g.pair ? 1 : (p.N + kTileRows - 1) / kTileRows;
   g.MT = g.KB;
   g.h = static_cast<int>(blockIdx.x) % p.H;
@@ -189,11 +192,11 @@ __device__ __forceinline__ void bwd_group(bool has_bias, bool has_mask, const ui
 // ------------------------------------------------------------------------------------------------
 // The two compute warpgroups
 // ------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool kPair>
 __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t smem_base,
                                  uint32_t bars, uint32_t tmem, const WaitCtx& ctx,
                                  float& dscale_acc) {
-  const BwdGeom g = bwd_geom(p);
+  const BwdGeom g = bwd_geom<kPair>(p);
   if (g.njobs == 0) return;
   const uint32_t tid = threadIdx.x;
   const uint32_t wg = tid >> 7, lt = tid & 127u;
@@ -594,10 +597,10 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
 //   per tile:  Q row normalised in place; delta = dO . O and lse * log2(e) of the row
 // The O row comes straight from global memory, fetched one tile ahead into registers.
 // ------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool kPair>
 __device__ void bwd_prepare_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t smem_base,
                                  uint32_t bars, const WaitCtx& ctx) {
-  const BwdGeom g = bwd_geom(p);
+  const BwdGeom g = bwd_geom<kPair>(p);
   if (g.njobs == 0) return;
   const uint32_t lt = threadIdx.x & 127u;
   auto bar = [&](int i) { return bars + 8u * i; };
@@ -675,10 +678,10 @@ __device__ void bwd_prepare_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
 // ------------------------------------------------------------------------------------------------
 // MMA issuer (one thread)
 // ------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool kPair>
 __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
                              const WaitCtx& ctx) {
-  const BwdGeom g = bwd_geom(p);
+  const BwdGeom g = bwd_geom<kPair>(p);
   if (g.njobs == 0) return;
   constexpr uint32_t fmt = Elem<T>::kFmt;
   auto bar = [&](int i) { return bars + 8u * i; };
@@ -841,10 +844,10 @@ __device__ void bwd_mma_role(const BwdParams& p, uint32_t smem_base, uint32_t ba
 // written out as straight-line code with as few waits and commits as the dependencies allow.
 // Per step w one barrier announces the scores (kbStFull + 2 w) and one P^T / dS^T (kbPtFull + 2 w).
 // ------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool kPair>
 __device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
                                   const WaitCtx& ctx) {
-  const BwdGeom g = bwd_geom(p);
+  const BwdGeom g = bwd_geom<kPair>(p);
   if (g.njobs == 0) return;
   constexpr uint32_t fmt = Elem<T>::kFmt;
   auto bar = [&](int i) { return bars + 8u * i; };
@@ -958,8 +961,9 @@ __device__ void bwd_mma_role_pair(const BwdParams& p, uint32_t smem_base, uint32
 //   warp 10  bias^T / mask^T chunks for warpgroup 0        warp 11  the same for warpgroup 1
 // Every stream issues its loads in the order in which they are consumed.
 // ------------------------------------------------------------------------------------------------
+template <bool kPair>
 __device__ void bwd_load_main(const BwdParams& p, uint32_t smem_base, uint32_t bars, const WaitCtx& ctx) {
-  const BwdGeom g = bwd_geom(p);
+  const BwdGeom g = bwd_geom<kPair>(p);
   if (g.njobs == 0) return;
   auto bar = [&](int i) { return bars + 8u * i; };
   TileIt it{0, 0, 0};
@@ -1011,8 +1015,9 @@ __device__ void bwd_load_main(const BwdParams& p, uint32_t smem_base, uint32_t b
 
 // Tables of warpgroup w.  Pair mode: the warpgroup works on chunk w of both units, one table stage
 // per tile.  Otherwise: the existing chunks of step w of every tile, in order.
+template <bool kPair>
 __device__ void bwd_load_tables(const BwdParams& p, uint32_t smem_base, uint32_t bars, const WaitCtx& ctx, int w) {
-  const BwdGeom g = bwd_geom(p);
+  const BwdGeom g = bwd_geom<kPair>(p);
   if (g.njobs == 0 || !(p.has_bias || p.has_mask)) return;
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t NBM = p.n_bm_stages;
@@ -1049,7 +1054,7 @@ __device__ void bwd_load_tables(const BwdParams& p, uint32_t smem_base, uint32_t
 }
 
 // ------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool kPair>
 __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t tid = threadIdx.x;
@@ -1069,7 +1074,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
     ctrl_words[1] = 0u;
     for (int i = 0; i < kBwdNumBars; ++i) {
       // jobs of a single tile: dQ is written by warpgroup 0 alone
-      const bool single = p.pair_mode || p.N <= kTileRows;
+      const bool single = kPair || p.N <= kTileRows;
       uint32_t count = 1u;
       if (i >= kbKvReady && i < kbKvFree) count = 128u;   // the preparing warpgroup
       else if (i >= kbKvFree && i < kbQdoFull) count = 257u;
@@ -1124,19 +1129,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
   // 512 threads start with 128 registers each; the compute warpgroups take what the others give up
   if (warp < 8) {
     reg_alloc<176>();
-    bwd_compute_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, dscale_acc);
+    bwd_compute_role<T, kPair>(p, smem_raw, smem_base, bars, tmem, ctx, dscale_acc);
   } else if (warp < 12) {
     reg_dealloc<80>();
     if (lane == 0) {
       if (warp == 8) {
-        if (p.pair_mode) bwd_mma_role_pair<T>(p, smem_base, bars, tmem, ctx);
-        else bwd_mma_role<T>(p, smem_base, bars, tmem, ctx);
-      } else if (warp == 9) bwd_load_main(p, smem_base, bars, ctx);
-      else bwd_load_tables(p, smem_base, bars, ctx, static_cast<int>(warp) - 10);
+        if constexpr (kPair) bwd_mma_role_pair<T, true>(p, smem_base, bars, tmem, ctx);
+        else bwd_mma_role<T, false>(p, smem_base, bars, tmem, ctx);
+      } else if (warp == 9) bwd_load_main<kPair>(p, smem_base, bars, ctx);
+      else bwd_load_tables<kPair>(p, smem_base, bars, ctx, static_cast<int>(warp) - 10);
     }
   } else {
     reg_dealloc<80>();
-    bwd_prepare_role<T>(p, smem_raw, smem_base, bars, ctx);
+    bwd_prepare_role<T, kPair>(p, smem_raw, smem_base, bars, ctx);
   }
   __syncwarp();
   // deterministic CTA-wide sum of the dLogitScale contributions
@@ -1173,8 +1178,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_kernel(const __grid_consta
   if (warp == 8) tmem_dealloc(tmem, kBwdTmemCols);
 }
 
-template __global__ void bwd_kernel<__nv_bfloat16>(const __grid_constant__ BwdParams);
-template __global__ void bwd_kernel<__half>(const __grid_constant__ BwdParams);
+template __global__ void bwd_kernel<__nv_bfloat16, false>(const __grid_constant__ BwdParams);
+template __global__ void bwd_kernel<__nv_bfloat16, true>(const __grid_constant__ BwdParams);
+template __global__ void bwd_kernel<__half, false>(const __grid_constant__ BwdParams);
+template __global__ void bwd_kernel<__half, true>(const __grid_constant__ BwdParams);
 
 cudaError_t launch_bwd(const BwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream) {
   auto go = [&](auto kern) -> cudaError_t {
@@ -1184,7 +1191,8 @@ cudaError_t launch_bwd(const BwdParams& p, int dtype_is_bf16, int grid, cudaStre
     kern<<<grid, kBwdThreads, p.smem_bytes, stream>>>(p);
     return cudaGetLastError();
   };
-  return dtype_is_bf16 ? go(bwd_kernel<__nv_bfloat16>) : go(bwd_kernel<__half>);
+  if (p.pair_mode) return dtype_is_bf16 ? go(bwd_kernel<__nv_bfloat16, true>) : go(bwd_kernel<__half, true>);
+  return dtype_is_bf16 ? go(bwd_kernel<__nv_bfloat16, false>) : go(bwd_kernel<__half, false>);
 }
 
 }  // namespace fwa2
