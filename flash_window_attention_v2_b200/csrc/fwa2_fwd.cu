@@ -41,12 +41,15 @@ struct FwdShape {
   int N, H, U, pair, MT, KS, rows_kv;
 };
 
+// kPair is a template parameter of the kernel: a launch runs code specialised for its mode and the
+// instruction cache holds none of the other mode's branches.
+template <bool kPair>
 __device__ __forceinline__ FwdShape fwd_shape(const FwdParams& p) {
   FwdShape s;
   s.N = p.N;
   s.H = p.H;
   s.U = p.BW * p.H;
-  s.pair = p.pair_mode;
+  s.pair = kPair ? 1 : 0;
   s.MT = s.pair ? 1 : (p.N + kTileRows - 1) / kTileRows;
   s.KS = s.pair ? 1 : (p.N + kStepCols - 1) / kStepCols;
   s.rows_kv = s.pair ? 128 : ((p.N + 63) / 64) * 64;
@@ -56,10 +59,10 @@ __device__ __forceinline__ FwdShape fwd_shape(const FwdParams& p) {
 // ------------------------------------------------------------------------------------------------
 // Softmax warps
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool kPTmem>
+template <typename T, bool kPTmem, bool kPair>
 __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_t bars,
                                  uint32_t tmem, const WaitCtx& ctx, const float* scale_tab) {
-  const FwdShape sh = fwd_shape(p);
+  const FwdShape sh = fwd_shape<kPair>(p);
   const uint32_t tid = threadIdx.x;          // 0..127 = row of the tile
   const uint32_t hf = tid >> 6;
   const uint32_t lane_base = ((tid >> 5) * 32u) << 16;
@@ -456,10 +459,10 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
 // ------------------------------------------------------------------------------------------------
 // MMA issuer (one thread)
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool kPTmem>
+template <typename T, bool kPTmem, bool kPair>
 __device__ void fwd_mma_role(const FwdParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
                              const WaitCtx& ctx) {
-  const FwdShape sh = fwd_shape(p);
+  const FwdShape sh = fwd_shape<kPair>(p);
   constexpr uint32_t fmt = Elem<T>::kFmt;
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t idesc_pv = make_idesc(fmt, 128, 32, 0, 1);
@@ -539,9 +542,10 @@ __device__ void fwd_mma_role(const FwdParams& p, uint32_t smem_base, uint32_t ba
 // job when two K/V stages fit, and (b) the bias / mask table chunks, which stay a few chunks
 // ahead of the softmax warps.
 // ------------------------------------------------------------------------------------------------
+template <bool kPair>
 __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t bars,
                               const WaitCtx& ctx) {
-  const FwdShape sh = fwd_shape(p);
+  const FwdShape sh = fwd_shape<kPair>(p);
   auto bar = [&](int i) { return bars + 8u * i; };
   const bool any_table = p.has_bias || p.has_mask;
   const uint32_t table_bytes =
@@ -676,7 +680,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
 }
 
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool kPTmem>
+template <typename T, bool kPTmem, bool kPair>
 __global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_constant__ FwdParams p) {
   // No static shared memory: the dynamic window then starts 1024-byte aligned, which the
   // swizzled tiles need; checked below.
@@ -725,10 +729,10 @@ __global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_consta
   WaitCtx ctx{&ctrl_words[1], p.status, (p.trace.buf != nullptr && p.trace.cap >= 700) ? p.trace.buf + 2ll * p.trace.cap + 500 : nullptr};
 
   if (warp < 4) {
-    fwd_softmax_role<T, kPTmem>(p, smem_base, bars, tmem, ctx, scale_tab);
+    fwd_softmax_role<T, kPTmem, kPair>(p, smem_base, bars, tmem, ctx, scale_tab);
   } else if (lane == 0) {
-    if (warp == 4) fwd_mma_role<T, kPTmem>(p, smem_base, bars, tmem, ctx);
-    else fwd_load_role(p, smem_base, bars, ctx);
+    if (warp == 4) fwd_mma_role<T, kPTmem, kPair>(p, smem_base, bars, tmem, ctx);
+    else fwd_load_role<kPair>(p, smem_base, bars, ctx);
   }
   __syncwarp();
   tc_fence_before();
@@ -743,10 +747,14 @@ __global__ void __launch_bounds__(kFwdThreads, 2) fwd_kernel(const __grid_consta
   if (warp == 4) tmem_dealloc(tmem, kFwdTmemCols);
 }
 
-template __global__ void fwd_kernel<__nv_bfloat16, true>(const __grid_constant__ FwdParams);
-template __global__ void fwd_kernel<__nv_bfloat16, false>(const __grid_constant__ FwdParams);
-template __global__ void fwd_kernel<__half, true>(const __grid_constant__ FwdParams);
-template __global__ void fwd_kernel<__half, false>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__nv_bfloat16, true, true>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__nv_bfloat16, true, false>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__nv_bfloat16, false, true>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__nv_bfloat16, false, false>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__half, true, true>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__half, true, false>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__half, false, true>(const __grid_constant__ FwdParams);
+template __global__ void fwd_kernel<__half, false, false>(const __grid_constant__ FwdParams);
 
 cudaError_t launch_fwd(const FwdParams& p, int dtype_is_bf16, int p_in_tmem, int grid,
                        cudaStream_t stream) {
@@ -757,10 +765,14 @@ cudaError_t launch_fwd(const FwdParams& p, int dtype_is_bf16, int p_in_tmem, int
     kern<<<grid, kFwdThreads, p.smem_bytes, stream>>>(p);
     return cudaGetLastError();
   };
-  if (dtype_is_bf16) {
-    return p_in_tmem ? go(fwd_kernel<__nv_bfloat16, true>) : go(fwd_kernel<__nv_bfloat16, false>);
-  }
-  return p_in_tmem ? go(fwd_kernel<__half, true>) : go(fwd_kernel<__half, false>);
+  auto by_mode = [&](auto pair_tag) -> cudaError_t {
+    constexpr bool kPair = decltype(pair_tag)::value;
+    if (dtype_is_bf16) {
+      return p_in_tmem ? go(fwd_kernel<__nv_bfloat16, true, kPair>) : go(fwd_kernel<__nv_bfloat16, false, kPair>);
+    }
+    return p_in_tmem ? go(fwd_kernel<__half, true, kPair>) : go(fwd_kernel<__half, false, kPair>);
+  };
+  return p.pair_mode ? by_mode(std::true_type{}) : by_mode(std::false_type{});
 }
 
 }  // namespace fwa2

@@ -136,14 +136,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   // Inline polling loop, kept short (it exists at every wait site of an instruction-cache-bound
   // kernel): on expiry only the CTA's abort word is set, to (site << 8 | kind); the kernel copies
   // it into the caller's status word at its end (report_abort()).
-  const long long t0 = clock64();
+  // (32-bit clock: the limit is below 2^32 cycles and the clock is read every 256 polls)
+  const uint32_t t0 = static_cast<uint32_t>(clock());
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (kRelaxed) __nanosleep(200);
     if ((++spins & 0xFFu) == 0) {
       if (*ctx.abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (static_cast<uint32_t>(clock()) - t0 > static_cast<uint32_t>(kWaitLimitCycles)) {
         *ctx.abort_flag = (site << 8) | kStatusTimeout;
         return false;
       }
