@@ -56,6 +56,17 @@ __device__ __forceinline__ FwdShape fwd_shape(const FwdParams& p) {
   return s;
 }
 
+// (window, head, mask plane) of the one or two units of a job; recomputed when the job changes.
+// Out of line: four integer divisions by run-time values, needed at four places of the producer.
+struct JobUnits { int bw0, bw1, h0, h1, mw0, mw1; };
+static __device__ __noinline__ JobUnits job_units(int job, bool pair, int H, int nW) {
+  JobUnits u;
+  const int u0 = pair ? 2 * job : job, u1 = pair ? 2 * job + 1 : job;
+  u.bw0 = u0 / H; u.h0 = u0 - u.bw0 * H; u.mw0 = nW > 0 ? u.bw0 % nW : 0;
+  u.bw1 = u1 / H; u.h1 = u1 - u.bw1 * H; u.mw1 = nW > 0 ? u.bw1 % nW : 0;
+  return u;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Softmax warps
 // ------------------------------------------------------------------------------------------------
@@ -560,16 +571,8 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
   bool a_done = a_job >= p.n_jobs;
   bool b_done = !any_table || b_job >= p.n_jobs;
 
-  // (window, head, mask plane) of the one or two units of a job; recomputed when the job changes
-  struct JobUnits { int bw0, bw1, h0, h1, mw0, mw1; };
-  auto job_units = [&](int job) {
-    JobUnits u;
-    const int u0 = sh.pair ? 2 * job : job, u1 = sh.pair ? 2 * job + 1 : job;
-    u.bw0 = u0 / sh.H; u.h0 = u0 - u.bw0 * sh.H; u.mw0 = p.has_mask ? u.bw0 % p.nW : 0;
-    u.bw1 = u1 / sh.H; u.h1 = u1 - u.bw1 * sh.H; u.mw1 = p.has_mask ? u.bw1 % p.nW : 0;
-    return u;
-  };
-  JobUnits a_u = job_units(a_job), b_u = job_units(b_job);
+  JobUnits a_u = job_units(a_job, kPair, sh.H, p.has_mask ? p.nW : 0);
+  JobUnits b_u = job_units(b_job, kPair, sh.H, p.has_mask ? p.nW : 0);
 
   long long t0 = clock64();
   uint32_t idle = 0;
@@ -617,7 +620,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
             a_kv.advance();
             a_job += gridDim.x;
             a_done = a_job >= p.n_jobs;
-            a_u = job_units(a_job);
+            a_u = job_units(a_job, kPair, sh.H, p.has_mask ? p.nW : 0);
           }
           progress = true;
         }
@@ -651,7 +654,7 @@ __device__ void fwd_load_role(const FwdParams& p, uint32_t smem_base, uint32_t b
               b_mt = 0;
               b_job += gridDim.x;
               b_done = b_job >= p.n_jobs;
-              b_u = job_units(b_job);
+              b_u = job_units(b_job, kPair, sh.H, p.has_mask ? p.nW : 0);
             }
           }
         }
