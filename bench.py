@@ -381,7 +381,7 @@ def main():
     # ------------------------------------------------------------------ roofline of the dominant kernel
     # DRAM bytes per launch of the dominant kernel from the ncu captures summarised in profiles/
     # (dram__bytes_read.sum + dram__bytes_write.sum); None for workloads that were not captured
-    ncu_traffic = {"cfg2": 369.3e6, "cfg3": 198.7e6}
+    ncu_traffic = {"cfg2": 368.9e6, "cfg3": 198.7e6}
     bwd_bytes = w.algorithmic_bytes(fwd=False, bwd=True)
     ach = bwd_bytes / (kt["bwd_main"] * 1e-3) / 1e9
     roofline = dict(bound="hbm", kernel="bwd_kernel", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s",
