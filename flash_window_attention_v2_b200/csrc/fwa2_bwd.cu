@@ -491,10 +491,10 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           uint32_t sa[8], da[8], sb[8], db8[8];
           tmem_ld8(t_s, sa);
           tmem_ld8(t_d, da);
+          tmem_wait_ld();
 #pragma unroll 1
           for (uint32_t gq = 0; gq < 4u; ++gq) {
             uint32_t pw[4], dw[4];
-            tmem_wait_ld();
             if (gq + 1u < 4u) {
               tmem_ld8(t_s + 8u * (gq + 1u), sb);
               tmem_ld8(t_d + 8u * (gq + 1u), db8);
@@ -506,6 +506,7 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
             tmem_st4(t_s + 4u * gq, pw);
             tmem_st4(t_d + 4u * gq, dw);
             sts128(ds_base + (((4u * c + gq) ^ ds_sw) << 4), dw);
+            tmem_wait_ld();   // the next group's registers may be read from here on
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               sa[i] = sb[i];

@@ -121,10 +121,17 @@ __global__ void __launch_bounds__(32 * kReduceLanes) reduce_partials_kernel(cons
       }
     }
   }
-  if (blockIdx.x == 0 && blockIdx.y == 0 && tx == 0 && ty == 0 && p.dscale_partial != nullptr) {
+  // dLogitScale of head h: one warp, lane l adds slots l, l + 32, ... in ascending order, then a fixed
+  // shuffle tree (all the loads of a lane are in flight together: a single thread walking the
+  // list was the longest dependency chain of this kernel)
+  if (blockIdx.x == 0 && blockIdx.y == 0 && ty == 0 && p.dscale_partial != nullptr) {
     float s = 0.f;
-    for (int sl = 0; sl < p.nslots; ++sl) s += p.dscale_partial[sl * p.H + h];
-    if (p.out_f32 != nullptr) {
+    for (int sl = tx; sl < p.nslots; sl += 32) s += p.dscale_partial[sl * p.H + h];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+    if (tx != 0) {
+      // lane 0 writes
+    } else if (p.out_f32 != nullptr) {
       p.out_f32[static_cast<long long>(p.H) * p.N * p.N + h] = s;
     } else if (p.dscale != nullptr) {
       static_cast<uint16_t*>(p.dscale)[h] = to_raw16<T>(s * clamp_gate<T>(p.logit_scale, h));
