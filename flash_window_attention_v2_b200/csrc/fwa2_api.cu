@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <mutex>
 
 #include "fwa2_common.cuh"
 
@@ -13,6 +14,8 @@ namespace fwa2 {
 cudaError_t launch_fwd(const FwdParams& p, int dtype_is_bf16, int p_in_tmem, int grid,
                        cudaStream_t stream);
 cudaError_t launch_bwd(const BwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
+cudaError_t launch_bwd_quad(const QuadParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
+int quad_max_active_clusters(int dtype_is_bf16, int cluster, uint32_t smem_bytes);
 cudaError_t launch_transpose_tables(const void* bias, long long bias_pitch, void* bias_t,
                                     const void* mask, long long mask_pitch, void* mask_t, int n_bias,
                                     int n_mask, int n, int dst_pitch, cudaStream_t stream);
@@ -136,19 +139,26 @@ size_t align256(size_t x) { return (x + 255u) & ~static_cast<size_t>(255u); }
 
 // How the backward pass carves up its workspace and its grid.
 struct BwdPlan {
-  int pair, nslots, grid, n_bufs, table_pitch, db_pitch;
+  int pair, quad, cluster, nslots, grid, n_bufs, table_pitch, db_pitch;
   size_t off_bias_t, off_mask_t, off_db, off_dscale, total;
 };
 
+// Windows of 65 to 256 tokens go to the cluster kernel (fwa2_bwd_quad.cu) unless the caller asks
+// for the general one.
+bool wants_quad(int n, int variant) { return n > 64 && n <= 256 && (variant & FWA2_BWD_GENERAL_KERNEL) == 0; }
+
 BwdPlan make_bwd_plan(int bw, int heads, int n, int n_windows, bool has_bias, bool has_mask,
-                      int sm_count) {
+                      int sm_count, bool quad) {
   BwdPlan pl;
   pl.pair = n <= 64;
-  const int per_head = sm_count / heads > 0 ? sm_count / heads : 1;
+  pl.quad = quad ? 1 : 0;
+  pl.cluster = quad ? (n > kTileRows ? 4 : 1) : 1;
+  const int groups = sm_count / pl.cluster;   // CTAs, or clusters, that can be resident
+  const int per_head = groups / heads > 0 ? groups / heads : 1;
   const int jobs = pl.pair ? (bw + 1) / 2 : bw;
   pl.nslots = per_head < jobs ? per_head : jobs;
-  pl.grid = pl.nslots * heads;
-  pl.n_bufs = pl.grid * (pl.pair ? 2 : 1);
+  pl.grid = pl.nslots * heads * pl.cluster;
+  pl.n_bufs = pl.nslots * heads * (pl.pair ? 2 : 1);
   pl.table_pitch = ((n + 7) / 8) * 8;
   pl.db_pitch = ((n + 31) / 32) * 32;
   size_t off = 0;
@@ -159,9 +169,51 @@ BwdPlan make_bwd_plan(int bw, int heads, int n, int n_windows, bool has_bias, bo
   pl.off_db = off;
   if (has_bias) off += align256(static_cast<size_t>(pl.n_bufs) * pl.db_pitch * pl.db_pitch * 4u);
   pl.off_dscale = off;
-  off += align256(static_cast<size_t>(pl.grid) * 4u);
+  off += align256(static_cast<size_t>(pl.nslots) * heads * pl.cluster * 4u);
   pl.total = off;
   return pl;
+}
+
+// Shared-memory layout of the cluster kernel; false if it does not fit.
+bool quad_smem_plan(QuadParams& p, uint32_t budget) {
+  const uint32_t mask_b = p.has_mask ? 2u * 32768u : 0u, bias_b = p.has_bias ? 32768u : 0u;
+  const uint32_t recv_b = p.cluster > 1 ? 3u * 64u * 128u : 0u;
+  auto total = [&](uint32_t ns) {
+    return ns * 32768u + mask_b + bias_b + 32768u + recv_b + 4096u + ns * 1024u + kCtrlBytes;
+  };
+  uint32_t ns = 3;
+  if (total(ns) > budget) ns = 2;
+  if (total(ns) > budget) return false;
+  p.n_stages = static_cast<int>(ns);
+  p.n_mask_stages = 2;
+  p.off_stage = 0;
+  p.off_mask = p.off_stage + ns * 32768u;
+  p.off_bias = p.off_mask + mask_b;
+  p.off_ds = p.off_bias + bias_b;
+  p.off_recv = p.off_ds + 32768u;
+  p.off_ident = p.off_recv + recv_b;
+  p.off_rowstats = p.off_ident + 4096u;
+  p.off_ctrl = p.off_rowstats + ns * 1024u;
+  p.smem_bytes = p.off_ctrl + kCtrlBytes;
+  return true;
+}
+
+// Resident clusters per device for the cluster kernel, looked up once per
+// (device, dtype, cluster size, shared-memory size).
+int cached_max_clusters(int dtype_is_bf16, int cluster, uint32_t smem_bytes) {
+  struct Entry { int dev, bf16, cluster; uint32_t smem; int value; };
+  static std::mutex mu;
+  static Entry cache[32];
+  static int used = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used; ++i)
+    if (cache[i].dev == dev && cache[i].bf16 == dtype_is_bf16 && cache[i].cluster == cluster && cache[i].smem == smem_bytes)
+      return cache[i].value;
+  const int v = quad_max_active_clusters(dtype_is_bf16, cluster, smem_bytes);
+  if (v > 0 && used < 32) cache[used++] = Entry{dev, dtype_is_bf16, cluster, smem_bytes, v};
+  return v;
 }
 
 }  // namespace
@@ -279,7 +331,13 @@ extern "C" size_t fwa2_bwd_workspace_bytes(int32_t bw, int32_t heads, int32_t n,
   if (bw <= 0 || heads <= 0 || n <= 0 || n > 640 || (has_mask && n_windows <= 0)) return 0;
   const DeviceInfo dev = device_info();
   const int sms = dev.ok ? dev.sm_count : 148;
-  return make_bwd_plan(bw, heads, n, n_windows, has_bias != 0, has_mask != 0, sms).total;
+  // enough for either kernel that serves this window size
+  size_t need = make_bwd_plan(bw, heads, n, n_windows, has_bias != 0, has_mask != 0, sms, false).total;
+  if (wants_quad(n, 0)) {
+    const size_t q = make_bwd_plan(bw, heads, n, n_windows, has_bias != 0, has_mask != 0, sms, true).total;
+    if (q > need) need = q;
+  }
+  return need;
 }
 
 extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
@@ -299,22 +357,143 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   if (has_bias && (a->bias_row_stride < a->n)) return FWA2_ERR_STRIDE;
   if (has_mask && (a->mask_row_stride < a->n)) return FWA2_ERR_STRIDE;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int is_bf16 = a->dtype == FWA2_BF16;
 
   const DeviceInfo dev = device_info();
   if (!dev.ok) return FWA2_ERR_LAUNCH;
-  BwdPlan pl = make_bwd_plan(a->bw, a->heads, a->n, a->n_windows, has_bias, has_mask, dev.sm_count);
-  if (a->max_ctas > 0 && pl.grid > a->max_ctas) {
-    // a smaller grid keeps the same workspace layout (it only uses a prefix of it)
-    int ns = a->max_ctas / a->heads;
-    if (ns < 1) ns = 1;
-    if (ns < pl.nslots) { pl.nslots = ns; pl.grid = ns * a->heads; }
-  }
+  const bool quad = wants_quad(a->n, a->variant);
+  BwdPlan pl = make_bwd_plan(a->bw, a->heads, a->n, a->n_windows, has_bias, has_mask, dev.sm_count, quad);
   if (a->workspace == nullptr || a->workspace_bytes < pl.total ||
       (reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0)
     return FWA2_ERR_WORKSPACE;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   void* bias_t = ws + pl.off_bias_t;
   void* mask_t = ws + pl.off_mask_t;
+  float* db_partial = (has_bias && (a->variant & FWA2_BWD_SKIP_DBIAS) == 0) ? reinterpret_cast<float*>(ws + pl.off_db) : nullptr;
+  float* dscale_partial = reinterpret_cast<float*>(ws + pl.off_dscale);
+
+  // Everything that can fail is checked and every descriptor is encoded before the first launch:
+  // a rejected call leaves the workspace and the outputs untouched.
+  BwdParams p;
+  QuadParams qp;
+  std::memset(&p, 0, sizeof(p));
+  std::memset(&qp, 0, sizeof(qp));
+  if (quad) {
+    if ((rc = encode_rows4(&qp.tm_q, a->q, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+    if ((rc = encode_rows4(&qp.tm_k, a->k, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+    if ((rc = encode_rows4(&qp.tm_v, a->v, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+    if ((rc = encode_rows4(&qp.tm_do, a->dout, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+    if (has_bias &&
+        (rc = encode_table3(&qp.tm_biasT, bias_t, a->dtype, a->heads, a->n, a->n, pl.table_pitch)) != FWA2_OK)
+      return rc;
+    if (has_mask &&
+        (rc = encode_table3(&qp.tm_maskT, mask_t, a->dtype, a->n_windows, a->n, a->n, pl.table_pitch)) != FWA2_OK)
+      return rc;
+    qp.q = a->q.ptr; qp.q_sbw = a->q.stride_bw; qp.q_sh = a->q.stride_h; qp.q_sn = a->q.stride_n;
+    qp.k = a->k.ptr; qp.k_sbw = a->k.stride_bw; qp.k_sh = a->k.stride_h; qp.k_sn = a->k.stride_n;
+    qp.o = a->o.ptr; qp.o_sbw = a->o.stride_bw; qp.o_sh = a->o.stride_h; qp.o_sn = a->o.stride_n;
+    qp.dq = a->dq.ptr; qp.dq_sbw = a->dq.stride_bw; qp.dq_sh = a->dq.stride_h; qp.dq_sn = a->dq.stride_n;
+    qp.dk = a->dk.ptr; qp.dk_sbw = a->dk.stride_bw; qp.dk_sh = a->dk.stride_h; qp.dk_sn = a->dk.stride_n;
+    qp.dv = a->dv.ptr; qp.dv_sbw = a->dv.stride_bw; qp.dv_sh = a->dv.stride_h; qp.dv_sn = a->dv.stride_n;
+    qp.lse = a->lse; qp.lse_sbw = a->lse_stride_bw; qp.lse_sh = a->lse_stride_h;
+    qp.scale = a->logit_scale; qp.scale_is_tensor = a->scale_is_tensor;
+    qp.db_partial = db_partial;
+    qp.db_pitch = pl.db_pitch;
+    qp.db_buf_stride = static_cast<long long>(pl.db_pitch) * pl.db_pitch;
+    qp.dscale_partial = dscale_partial;
+    qp.BW = a->bw; qp.H = a->heads; qp.N = a->n; qp.nW = has_mask ? a->n_windows : 1;
+    qp.has_bias = has_bias; qp.has_mask = has_mask;
+    qp.cluster = pl.cluster;
+    qp.status = static_cast<DeviceStatus*>(a->status);
+    qp.prof = (a->trace != nullptr && a->trace_entries >= 64) ? reinterpret_cast<unsigned long long*>(a->trace) : nullptr;
+    if (!quad_smem_plan(qp, static_cast<uint32_t>(dev.max_smem_optin))) return FWA2_ERR_SHAPE;
+    // no more clusters than the device holds at once (fewer clusters use a prefix of the
+    // workspace's partial buffers)
+    int max_clusters = cached_max_clusters(is_bf16, pl.cluster, qp.smem_bytes);
+    if (max_clusters <= 0) return FWA2_ERR_LAUNCH;
+    if (a->max_ctas > 0 && a->max_ctas / pl.cluster < max_clusters) max_clusters = a->max_ctas / pl.cluster;
+    int ns = max_clusters / a->heads;
+    if (ns < 1) ns = 1;
+    if (ns < pl.nslots) { pl.nslots = ns; pl.grid = ns * a->heads * pl.cluster; }
+    qp.nslots = pl.nslots;
+  } else {
+    if (a->max_ctas > 0 && pl.grid > a->max_ctas) {
+      // a smaller grid keeps the same workspace layout (it only uses a prefix of it)
+      int ns = a->max_ctas / a->heads;
+      if (ns < 1) ns = 1;
+      if (ns < pl.nslots) { pl.nslots = ns; pl.grid = ns * a->heads; }
+    }
+    // pair mode loads Q and dO in boxes of 32 rows, so that the queries of the two units can be
+    // interleaved in shared memory (see the kernel)
+    const int q_box_rows = pl.pair ? 32 : kBoxRows;
+    if ((rc = encode_rows4(&p.tm_q, a->q, a->dtype, a->bw, a->heads, a->n, q_box_rows)) != FWA2_OK) return rc;
+    if ((rc = encode_rows4(&p.tm_k, a->k, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+    if ((rc = encode_rows4(&p.tm_v, a->v, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
+    if ((rc = encode_rows4(&p.tm_do, a->dout, a->dtype, a->bw, a->heads, a->n, q_box_rows)) != FWA2_OK) return rc;
+    if (has_bias &&
+        (rc = encode_table3(&p.tm_biasT, bias_t, a->dtype, a->heads, a->n, a->n, pl.table_pitch)) != FWA2_OK)
+      return rc;
+    if (has_mask &&
+        (rc = encode_table3(&p.tm_maskT, mask_t, a->dtype, a->n_windows, a->n, a->n, pl.table_pitch)) != FWA2_OK)
+      return rc;
+
+    p.q = a->q.ptr; p.q_sbw = a->q.stride_bw; p.q_sh = a->q.stride_h; p.q_sn = a->q.stride_n;
+    p.k = a->k.ptr; p.k_sbw = a->k.stride_bw; p.k_sh = a->k.stride_h; p.k_sn = a->k.stride_n;
+    p.o = a->o.ptr; p.o_sbw = a->o.stride_bw; p.o_sh = a->o.stride_h; p.o_sn = a->o.stride_n;
+    p.dq = a->dq.ptr; p.dq_sbw = a->dq.stride_bw; p.dq_sh = a->dq.stride_h; p.dq_sn = a->dq.stride_n;
+    p.dk = a->dk.ptr; p.dk_sbw = a->dk.stride_bw; p.dk_sh = a->dk.stride_h; p.dk_sn = a->dk.stride_n;
+    p.dv = a->dv.ptr; p.dv_sbw = a->dv.stride_bw; p.dv_sh = a->dv.stride_h; p.dv_sn = a->dv.stride_n;
+    p.lse = a->lse; p.lse_sbw = a->lse_stride_bw; p.lse_sh = a->lse_stride_h;
+    p.scale = a->logit_scale; p.scale_is_tensor = a->scale_is_tensor;
+    p.db_partial = db_partial;
+    p.db_pitch = pl.db_pitch;
+    p.db_buf_stride = static_cast<long long>(pl.db_pitch) * pl.db_pitch;
+    p.dscale_partial = dscale_partial;
+    p.BW = a->bw; p.H = a->heads; p.N = a->n; p.nW = has_mask ? a->n_windows : 1;
+    p.has_bias = has_bias; p.has_mask = has_mask;
+    p.pair_mode = pl.pair;
+    p.nslots = pl.nslots;
+    p.status = static_cast<DeviceStatus*>(a->status);
+    p.trace.buf = reinterpret_cast<unsigned long long*>(a->trace);
+    p.trace.cap = a->trace != nullptr ? a->trace_entries : 0;
+
+    // ---- shared memory layout (one CTA per SM) ----
+    p.rows_kv = pl.pair ? 128 : ((a->n + 127) / 128) * 128;
+    p.kv_stage_bytes = 2u * static_cast<uint32_t>(p.rows_kv) * kRowBytes;
+    const uint32_t qdo_bytes = 3u * 4u * kBoxBytes;
+    const uint32_t bm_stage = 2u * kTableTileBytes;
+    const bool any_table = has_bias || has_mask;
+    auto total = [&](uint32_t nkv, uint32_t nds, uint32_t nbm) {
+      return nkv * p.kv_stage_bytes + qdo_bytes + nds * 32768u + (any_table ? 2u * nbm * bm_stage : 0u) +
+             4096u + nkv * static_cast<uint32_t>(p.rows_kv) * 4u + 3u * 1024u + kCtrlBytes;
+    };
+    const uint32_t budget = static_cast<uint32_t>(dev.max_smem_optin);
+    // Preference order.  Jobs of a single tile (windows of at most 128 tokens) release their
+    // K/V stage only in the epilogue that runs one tile late, so they want four stages to keep a
+    // whole tile of lead for the next load (see bwd_num_sets() in the kernel).
+    const uint32_t opts[][3] = {{4, 2, 2}, {4, 2, 1}, {4, 1, 2}, {3, 2, 2}, {3, 1, 2}, {2, 2, 2}, {2, 1, 2},
+                                {1, 2, 2}, {1, 1, 2}, {1, 1, 1}};
+    uint32_t nkv = 0, nds = 0, nbm = 0;
+    for (const auto& o : opts) {
+      if (o[0] >= 3 && p.rows_kv > 128) continue;
+      // one table stage per warpgroup is enough only in pair mode (one chunk per tile and warpgroup)
+      if (o[0] == 4 && o[2] == 1 && !pl.pair) continue;
+      if (total(o[0], o[1], o[2]) <= budget) { nkv = o[0]; nds = o[1]; nbm = o[2]; break; }
+    }
+    if (nkv == 0) return FWA2_ERR_SHAPE;
+    p.n_kv_stages = static_cast<int>(nkv);
+    p.n_ds_bufs = static_cast<int>(nds);
+    p.n_bm_stages = static_cast<int>(nbm);
+    p.off_kv = 0;
+    p.off_qdo = p.off_kv + nkv * p.kv_stage_bytes;
+    p.off_ds = p.off_qdo + qdo_bytes;
+    p.off_bm = p.off_ds + nds * 32768u;
+    p.off_ident = p.off_bm + (any_table ? 2u * nbm * bm_stage : 0u);
+    p.off_rk = p.off_ident + 4096u;
+    p.off_rowstats = p.off_rk + nkv * static_cast<uint32_t>(p.rows_kv) * 4u;
+    p.off_ctrl = p.off_rowstats + 3u * 1024u;
+    p.smem_bytes = p.off_ctrl + kCtrlBytes;
+  }
 
   cudaError_t e = cudaSuccess;
   if ((a->variant & FWA2_BWD_SKIP_TABLES) == 0) {
@@ -324,97 +503,23 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
     if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
   }
 
-  BwdParams p;
-  std::memset(&p, 0, sizeof(p));
-  // pair mode loads Q and dO in boxes of 32 rows, so that the queries of the two units can be
-  // interleaved in shared memory (see the kernel)
-  const int q_box_rows = pl.pair ? 32 : kBoxRows;
-  if ((rc = encode_rows4(&p.tm_q, a->q, a->dtype, a->bw, a->heads, a->n, q_box_rows)) != FWA2_OK) return rc;
-  if ((rc = encode_rows4(&p.tm_k, a->k, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
-  if ((rc = encode_rows4(&p.tm_v, a->v, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
-  if ((rc = encode_rows4(&p.tm_do, a->dout, a->dtype, a->bw, a->heads, a->n, q_box_rows)) != FWA2_OK) return rc;
-  if (has_bias &&
-      (rc = encode_table3(&p.tm_biasT, bias_t, a->dtype, a->heads, a->n, a->n, pl.table_pitch)) != FWA2_OK)
-    return rc;
-  if (has_mask &&
-      (rc = encode_table3(&p.tm_maskT, mask_t, a->dtype, a->n_windows, a->n, a->n, pl.table_pitch)) != FWA2_OK)
-    return rc;
-
-  p.q = a->q.ptr; p.q_sbw = a->q.stride_bw; p.q_sh = a->q.stride_h; p.q_sn = a->q.stride_n;
-  p.k = a->k.ptr; p.k_sbw = a->k.stride_bw; p.k_sh = a->k.stride_h; p.k_sn = a->k.stride_n;
-  p.o = a->o.ptr; p.o_sbw = a->o.stride_bw; p.o_sh = a->o.stride_h; p.o_sn = a->o.stride_n;
-  p.dq = a->dq.ptr; p.dq_sbw = a->dq.stride_bw; p.dq_sh = a->dq.stride_h; p.dq_sn = a->dq.stride_n;
-  p.dk = a->dk.ptr; p.dk_sbw = a->dk.stride_bw; p.dk_sh = a->dk.stride_h; p.dk_sn = a->dk.stride_n;
-  p.dv = a->dv.ptr; p.dv_sbw = a->dv.stride_bw; p.dv_sh = a->dv.stride_h; p.dv_sn = a->dv.stride_n;
-  p.lse = a->lse; p.lse_sbw = a->lse_stride_bw; p.lse_sh = a->lse_stride_h;
-  p.scale = a->logit_scale; p.scale_is_tensor = a->scale_is_tensor;
-  p.db_partial = (has_bias && (a->variant & FWA2_BWD_SKIP_DBIAS) == 0) ? reinterpret_cast<float*>(ws + pl.off_db) : nullptr;
-  p.db_pitch = pl.db_pitch;
-  p.db_buf_stride = static_cast<long long>(pl.db_pitch) * pl.db_pitch;
-  p.dscale_partial = reinterpret_cast<float*>(ws + pl.off_dscale);
-  p.BW = a->bw; p.H = a->heads; p.N = a->n; p.nW = has_mask ? a->n_windows : 1;
-  p.has_bias = has_bias; p.has_mask = has_mask;
-  p.pair_mode = pl.pair;
-  p.nslots = pl.nslots;
-  p.status = static_cast<DeviceStatus*>(a->status);
-  p.trace.buf = reinterpret_cast<unsigned long long*>(a->trace);
-  p.trace.cap = a->trace != nullptr ? a->trace_entries : 0;
-
-  // ---- shared memory layout (one CTA per SM) ----
-  p.rows_kv = pl.pair ? 128 : ((a->n + 127) / 128) * 128;
-  p.kv_stage_bytes = 2u * static_cast<uint32_t>(p.rows_kv) * kRowBytes;
-  const uint32_t qdo_bytes = 3u * 4u * kBoxBytes;
-  const uint32_t bm_stage = 2u * kTableTileBytes;
-  const bool any_table = has_bias || has_mask;
-  auto total = [&](uint32_t nkv, uint32_t nds, uint32_t nbm) {
-    return nkv * p.kv_stage_bytes + qdo_bytes + nds * 32768u + (any_table ? 2u * nbm * bm_stage : 0u) +
-           4096u + nkv * static_cast<uint32_t>(p.rows_kv) * 4u + 3u * 1024u + kCtrlBytes;
-  };
-  const uint32_t budget = static_cast<uint32_t>(dev.max_smem_optin);
-  // preference order; a job of one tile (at most 128 keys) wants three K/V stages, see
-  // bwd_num_sets() in the kernel
-  // Jobs of a single tile (windows of at most 128 tokens) release their K/V stage only in the
-  // epilogue that runs one tile late, so they want four stages to keep a whole tile of lead for
-  // the next load.
-  const uint32_t opts[][3] = {{4, 2, 2}, {4, 2, 1}, {4, 1, 2}, {3, 2, 2}, {3, 1, 2}, {2, 2, 2}, {2, 1, 2},
-                              {1, 2, 2}, {1, 1, 2}, {1, 1, 1}};
-  uint32_t nkv = 0, nds = 0, nbm = 0;
-  for (const auto& o : opts) {
-    if (o[0] >= 3 && p.rows_kv > 128) continue;
-    // one table stage per warpgroup is enough only in pair mode (one chunk per tile and warpgroup)
-    if (o[0] == 4 && o[2] == 1 && !pl.pair) continue;
-    if (total(o[0], o[1], o[2]) <= budget) { nkv = o[0]; nds = o[1]; nbm = o[2]; break; }
-  }
-  if (nkv == 0) return FWA2_ERR_SHAPE;
-  p.n_kv_stages = static_cast<int>(nkv);
-  p.n_ds_bufs = static_cast<int>(nds);
-  p.n_bm_stages = static_cast<int>(nbm);
-  p.off_kv = 0;
-  p.off_qdo = p.off_kv + nkv * p.kv_stage_bytes;
-  p.off_ds = p.off_qdo + qdo_bytes;
-  p.off_bm = p.off_ds + nds * 32768u;
-  p.off_ident = p.off_bm + (any_table ? 2u * nbm * bm_stage : 0u);
-  p.off_rk = p.off_ident + 4096u;
-  p.off_rowstats = p.off_rk + nkv * static_cast<uint32_t>(p.rows_kv) * 4u;
-  p.off_ctrl = p.off_rowstats + 3u * 1024u;
-  p.smem_bytes = p.off_ctrl + kCtrlBytes;
-
-  e = launch_bwd(p, a->dtype == FWA2_BF16, pl.grid, stream);
+  e = quad ? launch_bwd_quad(qp, is_bf16, pl.grid, stream) : launch_bwd(p, is_bf16, pl.grid, stream);
   if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
 
   if ((has_bias || a->scale_is_tensor) && (a->variant & FWA2_BWD_SKIP_REDUCE) == 0) {
     ReduceParams r;
     std::memset(&r, 0, sizeof(r));
-    r.db_partial = p.db_partial;
-    r.buf_stride = p.db_buf_stride;
+    r.db_partial = db_partial;
+    r.buf_stride = static_cast<long long>(pl.db_pitch) * pl.db_pitch;
     r.pitch = pl.db_pitch;
-    r.dscale_partial = a->scale_is_tensor ? p.dscale_partial : nullptr;
+    r.dscale_partial = a->scale_is_tensor ? dscale_partial : nullptr;
     r.H = a->heads; r.N = a->n; r.BW = a->bw; r.nslots = pl.nslots; r.pair = pl.pair;
+    r.dscale_slots = pl.nslots * pl.cluster;
     r.out_f32 = a->partial_out;
     r.dbias = a->dbias;
     r.dscale = a->dscale;
     r.logit_scale = a->logit_scale;
-    e = launch_reduce_partials(r, a->dtype == FWA2_BF16, stream);
+    e = launch_reduce_partials(r, is_bf16, stream);
     if (e != cudaSuccess) { g_last_cuda_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
   }
   return FWA2_OK;

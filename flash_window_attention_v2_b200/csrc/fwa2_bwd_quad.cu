@@ -1,0 +1,781 @@
+// Backward kernel for windows of 65 to 256 tokens.
+//
+// The N x N score matrix of a (window, head) unit is cut into 128 x 128 tiles: key block a, query
+// tile b.  A thread-block cluster of four CTAs (one CTA for windows of at most 128 tokens) works
+// on one unit at a time, CTA rank 2 a + b on tile (a, b), and every cluster keeps to one head.
+// What that buys:
+//   * the window-summed dBias tile of the CTA never leaves tensor memory: the tensor core adds
+//     every window's dS^T into it (dB^T += dS^T I) and it is written out once, at the end;
+//   * the CTA's tile of the bias table is loaded once and stays in shared memory;
+//   * every job of a CTA is the same short pipeline (two 64-query steps, five products).
+// What it costs: dV and dK of a key block are sums over the two query tiles, dQ of a query tile
+// over the two key blocks.  Each of those sums has exactly two terms, held by two CTAs of the
+// cluster; the two CTAs split the 128 rows between them, push the 64 rows they do not keep into
+// the other's shared memory (st.shared::cluster), and finish the rows they keep.  A sum of two
+// floats does not depend on the order, so the result is bitwise reproducible.
+//
+// As in the other backward kernel everything is computed transposed (keys on the tensor-memory
+// lanes): S^T = K^ Q^^T, dP^T = V dO^T, P^T and dS^T written back over them as packed 16-bit
+// pairs and used as tensor-memory A operands of dV += P^T dO, dK^ += dS^T Q^, dB^T += dS^T I; dS
+// also goes through shared memory for dQ^ += dS K^.
+//
+// Roles (640 threads): warps 0-3 / 4-7 compute warpgroups (step 0 / 1 of the tile, thread = key),
+// warps 8-11 epilogue warpgroup (the exchange and the epilogues, one job behind), warps 12-15
+// preparing warpgroup (normalises K and Q rows in place, delta, lse, one job ahead), warp 16
+// issues every tcgen05.mma, warp 17 is the TMA producer.
+// Replaces flash_win_attn_v2/kernels/attn_kernel_backward.py:6-51 and :84-564 for these sizes.
+#define FWA2_NORMALISE_ROLLED 1
+#define FWA2_WAIT_INLINE 1
+#include "fwa2_common.cuh"
+
+#include <cuda_runtime.h>
+
+namespace fwa2 {
+
+constexpr int kQuadThreads = 640;
+constexpr uint32_t kQuadTmemCols = 512;
+// Tensor-memory columns.  Step w: S^T at 128 w, dP^T at 128 w + 64 (64 queries each).
+constexpr uint32_t kQTmS = 0, kQTmDP = 64;
+constexpr uint32_t kQTmDV = 256, kQTmDK = 288, kQTmDQ = 320;
+constexpr uint32_t kQTmDB = 384;            // dB^T of the tile: 128 query columns (chunk c at 32 c)
+constexpr uint32_t kQStageBytes = 32768u;   // [K | V | Q | dO], 128 rows x 64 bytes each
+constexpr uint32_t kQTableBytes = 32768u;   // four chunks of (128 keys x 32 queries)
+constexpr uint32_t kQRecvPart = 64u * 128u; // 64 rows x 32 fp32 of one pushed accumulator
+
+enum QuadBar : int {
+  qbFull = 0, qbReady = 3, qbFree = 6,        // per stage (up to three)
+  qbMaskFull = 9, qbMaskFree = 11,            // per mask stage (two)
+  qbBiasFull = 13,
+  qbSFull = 14, qbPReady = 16,                // per step
+  qbAccFull = 18, qbAccFree = 19,
+  qbRecvFull = 20, qbRecvFree = 23,           // per pushed accumulator: 0 dV, 1 dK, 2 dQ
+  qbDsFree = 26,
+  kQuadNumBars = 27
+};
+
+struct QuadGeom {
+  int h, slot, count;
+  uint32_t rank, a, b;
+};
+__device__ __forceinline__ QuadGeom quad_geom(const QuadParams& p, uint32_t rank) {
+  QuadGeom g;
+  const int cid = static_cast<int>(blockIdx.x) / p.cluster;
+  g.h = cid % p.H;
+  g.slot = cid / p.H;
+  g.count = g.slot < p.BW ? (p.BW - g.slot + p.nslots - 1) / p.nslots : 0;
+  g.rank = rank;
+  g.a = rank >> 1;
+  g.b = rank & 1u;
+  return g;
+}
+
+__device__ __forceinline__ uint4 quad_ldg_v4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr));
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Eight queries of one key (= one thread):
+//   x = scale * cos + bias + mask,  p = exp2(x log2e - lse2),  ds = p (dP - delta).
+// Keys and queries past the end of the window need no special case.  Their rows of K, V, Q and dO
+// were zero-filled by the TMA loads and the tables read as zero there, so every value stays
+// finite; a query past the end has lse2 = +inf, hence p = ds = 0; a key past the end only feeds
+// rows of dK / dV / dB that are never stored, and its row of K^ is zero in the dQ product.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void quad_group(bool has_bias, bool has_mask, const uint32_t (&sv)[8],
+                                           const uint32_t (&dpv)[8], uint32_t bias_addr,
+                                           uint32_t mask_addr, const float* lse2, const float* delta,
+                                           float scale, uint32_t (&pw)[4], uint32_t (&dw)[4]) {
+  uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
+  if (has_bias) lds128(bias_addr, wb);
+  if (has_mask) lds128(mask_addr, wm);
+  const float4 la = *reinterpret_cast<const float4*>(lse2);
+  const float4 lb = *reinterpret_cast<const float4*>(lse2 + 4);
+  const float4 da = *reinterpret_cast<const float4*>(delta);
+  const float4 db = *reinterpret_cast<const float4*>(delta + 4);
+  const float l8[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+  const float d8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+#pragma unroll
+  for (int e2 = 0; e2 < 4; ++e2) {
+    const int e = 2 * e2;
+    const float x0 = fmaf(__uint_as_float(sv[e]), scale, Elem<T>::lo(wb[e2])) + Elem<T>::lo(wm[e2]);
+    const float x1 = fmaf(__uint_as_float(sv[e + 1]), scale, Elem<T>::hi(wb[e2])) + Elem<T>::hi(wm[e2]);
+    const float p0 = ex2f(fmaf(x0, kLog2e, -l8[e]));
+    const float p1 = ex2f(fmaf(x1, kLog2e, -l8[e + 1]));
+    const float s0 = p0 * (__uint_as_float(dpv[e]) - d8[e]);
+    const float s1 = p1 * (__uint_as_float(dpv[e + 1]) - d8[e + 1]);
+    pw[e2] = Elem<T>::pack(p0, p1);
+    dw[e2] = Elem<T>::pack(s0, s1);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The two compute warpgroups: step w (64 queries) of every job's tile, back to back
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ void quad_compute_role(const QuadParams& p, uint8_t* smem_ptr, uint32_t smem_base,
+                                  uint32_t bars, uint32_t tmem, const WaitCtx& ctx, uint32_t rank) {
+  const QuadGeom g = quad_geom(p, rank);
+  if (g.count == 0) return;
+  const uint32_t tid = threadIdx.x;
+  const uint32_t wg = tid >> 7, lt = tid & 127u;
+  const uint32_t lane_base = ((lt >> 5) * 32u) << 16;
+  const float scale = load_scale<T>(p.scale, p.scale_is_tensor, g.h);
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const float* rowstats = reinterpret_cast<const float*>(smem_ptr + p.off_rowstats);
+  const uint32_t NS = p.n_stages, NM = p.n_mask_stages;
+  const uint32_t ds_base = smem_base + p.off_ds + wg * 16384u + lt * 128u, ds_sw = lt & 7u;
+  const uint32_t tab_row = lt * 64u, tab_sw = (lt >> 1) & 3u;
+  const uint32_t tm_s = tmem + lane_base + wg * 128u + kQTmS;
+  const uint32_t tm_d = tmem + lane_base + wg * 128u + kQTmDP;
+
+  if (p.db_partial != nullptr) {
+    // the dB^T sums of my step's 64 query columns start from zero (the first product that adds to
+    // them is issued after this warpgroup's first P^T barrier)
+    uint32_t z[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) z[i] = 0u;
+#pragma unroll
+    for (uint32_t c = 0; c < 4u; ++c) tmem_st16(tmem + lane_base + kQTmDB + 64u * wg + 16u * c, z);
+    tmem_wait_st();
+    tc_fence_before();
+  }
+
+  Ring st(NS), mk(NM);
+#pragma unroll 1
+  for (int n = 0; n < g.count; ++n) {
+    const uint32_t par = static_cast<uint32_t>(n) & 1u;
+    if (!mbar_wait(bar(qbReady + st.stage), st.phase, ctx, 51)) return;     // row statistics
+    if (n == 0 && p.has_bias) {
+      if (!mbar_wait(bar(qbBiasFull), 0u, ctx, 57)) return;
+    }
+    if (p.has_mask) {
+      if (!mbar_wait(bar(qbMaskFull + mk.stage), mk.phase, ctx, 54)) return;
+    }
+    if (!mbar_wait(bar(qbSFull + wg), par, ctx, 52)) return;
+    tc_fence_after();
+    {
+      const float* lse2 = rowstats + st.stage * 256u + wg * 64u;
+      const float* delta = rowstats + st.stage * 256u + 128u + wg * 64u;
+      // eight groups of eight queries (two table chunks of 32); the scores of the next group are
+      // fetched from tensor memory while the current one is computed
+      uint32_t sa[8], da[8], sb[8], db8[8];
+      tmem_ld8(tm_s, sa);
+      tmem_ld8(tm_d, da);
+      tmem_wait_ld();
+#pragma unroll 1
+      for (uint32_t gi = 0; gi < 8u; ++gi) {
+        const uint32_t c = gi >> 2, gq = gi & 3u;
+        uint32_t pw[4], dw[4];
+        if (gi + 1u < 8u) {
+          tmem_ld8(tm_s + 8u * (gi + 1u), sb);
+          tmem_ld8(tm_d + 8u * (gi + 1u), db8);
+        }
+        const uint32_t chunk_off = (2u * wg + c) * static_cast<uint32_t>(kTableTileBytes) + tab_row + ((gq ^ tab_sw) << 4);
+        quad_group<T>(p.has_bias, p.has_mask, sa, da, smem_base + p.off_bias + chunk_off,
+                      smem_base + p.off_mask + mk.stage * kQTableBytes + chunk_off, lse2 + 8u * gi,
+                      delta + 8u * gi, scale, pw, dw);
+        // P^T and dS^T go back over the first 16 columns of this chunk's own S^T / dP^T columns
+        tmem_st4(tm_s + 32u * c + 4u * gq, pw);
+        tmem_st4(tm_d + 32u * c + 4u * gq, dw);
+        tmem_wait_ld();   // the next group's registers may be read from here on
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          sa[i] = sb[i];
+          da[i] = db8[i];
+        }
+      }
+    }
+    if (p.has_mask) {
+      mbar_arrive(bar(qbMaskFree + mk.stage));
+      mk.advance();
+    }
+    tmem_wait_st();
+    // dS also goes to shared memory (A operand of dQ^ += dS K^), but only now: the product that
+    // read the previous job's copy was issued while this step was being computed, so it is
+    // normally done and this wait costs nothing.  The packed words are read back from tensor
+    // memory (the loop above is rolled and cannot keep them in registers).
+    if (n > 0) {
+      if (!mbar_wait(bar(qbDsFree), par ^ 1u, ctx, 53)) return;
+    }
+#pragma unroll
+    for (uint32_t c = 0; c < 2u; ++c) {
+      uint32_t dsw[16];
+      tmem_ld16(tm_d + 32u * c, dsw);
+      tmem_wait_ld();
+#pragma unroll
+      for (uint32_t gq = 0; gq < 4u; ++gq) {
+        const uint32_t w4[4] = {dsw[4 * gq], dsw[4 * gq + 1], dsw[4 * gq + 2], dsw[4 * gq + 3]};
+        sts128(ds_base + (((4u * c + gq) ^ ds_sw) << 4), w4);
+      }
+    }
+    tc_fence_before();
+    fence_proxy_async_smem();
+    mbar_arrive(bar(qbPReady + wg));
+    st.advance();
+  }
+
+  // The dB^T sums of this CTA's tile leave tensor memory once, here, after the last product that
+  // fed them (it precedes the last dQ product, whose completion the last barrier phase signals).
+  // Warpgroup w writes the 64 query columns of its step; the partial buffer is laid out
+  // (query, key) like the result.
+  if (!mbar_wait(bar(qbDsFree), (static_cast<uint32_t>(g.count) & 1u) ^ 1u, ctx, 56)) return;
+  if (p.db_partial != nullptr) {
+    tc_fence_after();
+    const int key = static_cast<int>(g.a * kTileRows + lt);
+    const int cid = static_cast<int>(blockIdx.x) / p.cluster;
+    const int q0 = static_cast<int>(g.b * kTileRows + wg * kStepCols);
+    float* dst = p.db_partial + static_cast<long long>(cid) * p.db_buf_stride + key;
+    const bool key_ok = key < p.N;
+    const uint32_t t_db = tmem + lane_base + kQTmDB + 64u * wg;
+#pragma unroll 1
+    for (uint32_t gq = 0; gq < 8u; ++gq) {
+      uint32_t r[8];
+      tmem_ld8(t_db + 8u * gq, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int qi = q0 + static_cast<int>(8u * gq) + e;
+        if (key_ok && qi < p.N) dst[static_cast<long long>(qi) * p.db_pitch] = __uint_as_float(r[e]);
+      }
+    }
+    tc_fence_before();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The preparing warpgroup (thread = row), ahead of the compute warpgroups: K row and Q row of a
+// job normalised in place, delta = dO . O and lse * log2(e) of the query row.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ void quad_prepare_role(const QuadParams& p, uint8_t* smem_ptr, uint32_t smem_base,
+                                  uint32_t bars, const WaitCtx& ctx, uint32_t rank) {
+  const QuadGeom g = quad_geom(p, rank);
+  if (g.count == 0) return;
+  const uint32_t lt = threadIdx.x & 127u;
+  float* rowstats = reinterpret_cast<float*>(smem_ptr + p.off_rowstats);
+  const int ig = static_cast<int>(g.b * kTileRows + lt);
+  const bool row_ok = ig < p.N;
+  Ring st(p.n_stages);
+#pragma unroll 1
+  for (int n = 0; n < g.count; ++n) {
+    const int bw = g.slot + n * p.nslots;
+    uint4 o_row[4];
+    float lse = 0.f;
+    if (row_ok) {
+      const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) o_row[ch] = quad_ldg_v4(orow + ch * 8);
+      lse = __ldg(p.lse + bw * p.lse_sbw + g.h * p.lse_sh + ig);
+    }
+    const uint32_t base = smem_base + p.off_stage + st.stage * kQStageBytes;
+    if (!mbar_wait<true>(bars + 8u * (qbFull + st.stage), st.phase, ctx, 80)) return;
+    normalise_row<T>(base, lt);              // K^
+    normalise_row<T>(base + 16384u, lt);     // Q^
+    float l2 = INFINITY, dl = 0.f;
+    if (row_ok) {
+      float dlp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t wd[4];
+        lds128(base + 24576u + sw64_offset(lt, ch), wd);
+        const uint32_t wo[4] = {o_row[ch].x, o_row[ch].y, o_row[ch].z, o_row[ch].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          dlp[ch] = fmaf(Elem<T>::lo(wd[i]), Elem<T>::lo(wo[i]), dlp[ch]);
+          dlp[ch] = fmaf(Elem<T>::hi(wd[i]), Elem<T>::hi(wo[i]), dlp[ch]);
+        }
+      }
+      dl = (dlp[0] + dlp[1]) + (dlp[2] + dlp[3]);
+      l2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
+    }
+    rowstats[st.stage * 256u + lt] = l2;
+    rowstats[st.stage * 256u + 128u + lt] = dl;
+    fence_proxy_async_smem();
+    mbar_arrive(bars + 8u * (qbReady + st.stage));
+    st.advance();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The epilogue warpgroup (thread = row), behind the compute warpgroups: once the accumulators of
+// a job are complete, the exchange with the partner CTAs and the epilogues (Jacobian of the L2
+// normalisation, stores, dLogitScale).
+// Row r of an accumulator is tensor-memory lane r.  Of dV and dK (rows = keys of block a; the
+// other term of the sum is held by CTA (a, 1 - b) = rank ^ 1) this CTA keeps the rows of half
+// f = a ^ b and pushes the other half to that partner; of dQ (rows = queries of tile b; partner
+// (1 - a, b) = rank ^ 2) it keeps half 1 - f.  Every thread pushes first and finishes afterwards,
+// so no push ever waits behind a thread that waits for a push.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ void quad_epilogue_role(const QuadParams& p, uint8_t* smem_ptr, uint32_t smem_base,
+                                 uint32_t bars, uint32_t tmem, const WaitCtx& ctx, uint32_t rank,
+                                 float& dscale_acc) {
+  const QuadGeom g = quad_geom(p, rank);
+  if (g.count == 0) return;
+  const uint32_t lt = threadIdx.x & 127u;
+  const uint32_t lane_base = ((lt >> 5) * 32u) << 16;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const float scale = load_scale<T>(p.scale, p.scale_is_tensor, g.h);
+  const bool quad = p.cluster > 1;
+  const uint32_t half = lt >> 6;
+  const bool keeper = quad ? (half == (g.a ^ g.b)) : true;   // finishes its rows of dV and dK
+  const bool fin_q = quad ? !keeper : true;                  // finishes its row of dQ
+  const uint32_t recv_base = smem_base + p.off_recv;
+  const uint32_t row64 = lt & 63u, row_sw = lt & 7u;
+  const int krow = static_cast<int>(g.a * kTileRows + lt), qrow = static_cast<int>(g.b * kTileRows + lt);
+  const bool k_ok = krow < p.N, q_ok = qrow < p.N;
+
+#pragma unroll 1
+  for (int n = 0; n < g.count; ++n) {
+    const int bw = g.slot + n * p.nslots;
+    const uint32_t par = static_cast<uint32_t>(n) & 1u;
+    // the raw k / q rows for the Jacobians of this job's epilogue: requested first, used last
+    uint4 rawk[4], rawq[4];
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) rawk[ch] = rawq[ch] = make_uint4(0u, 0u, 0u, 0u);
+    if (keeper && k_ok) {
+      const uint16_t* src = static_cast<const uint16_t*>(p.k) + bw * p.k_sbw + g.h * p.k_sh + krow * p.k_sn;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) rawk[ch] = quad_ldg_v4(src + ch * 8);
+    }
+    if (fin_q && q_ok) {
+      const uint16_t* src = static_cast<const uint16_t*>(p.q) + bw * p.q_sbw + g.h * p.q_sh + qrow * p.q_sn;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) rawq[ch] = quad_ldg_v4(src + ch * 8);
+    }
+    // all three accumulators go to registers at once, so that the tensor core can start the next
+    // job's sums while the exchange and the epilogues run
+    if (!mbar_wait(bar(qbAccFull), par, ctx, 55)) return;
+    tc_fence_after();
+    uint32_t rv[32], rk[32], rq[32];
+    tmem_ld32(tmem + lane_base + kQTmDV, rv);
+    tmem_ld32(tmem + lane_base + kQTmDK, rk);
+    tmem_ld32(tmem + lane_base + kQTmDQ, rq);
+    tmem_wait_ld();
+    tc_fence_before();
+    mbar_arrive(bar(qbAccFree));
+
+    // X: 0 dV, 1 dK, 2 dQ
+    auto push = [&](const uint32_t (&r)[32], uint32_t X) -> bool {
+      const uint32_t partner = rank ^ (X == 2u ? 2u : 1u);
+      // the partner has read what I pushed for the previous job
+      if (!mbar_wait_cluster(bar(qbRecvFree + X), par ^ 1u, ctx, 58)) return false;
+      const uint32_t dst = cluster_map(recv_base + X * kQRecvPart + row64 * 128u, partner);
+#pragma unroll
+      for (uint32_t ch = 0; ch < 8u; ++ch) st_cluster_v4(dst + ((ch ^ row_sw) << 4), &r[4 * ch]);
+      mbar_arrive_cluster(cluster_map(bar(qbRecvFull + X), partner));
+      return true;
+    };
+    // rows of dV are stored as they are; rows of dK^ / dQ^ go through the Jacobian of the
+    // L2 normalisation: dx = scale (dX' - x^ (x^ . dX')) / |x| from the raw row x
+    auto finish = [&](uint32_t (&r)[32], uint32_t X, const uint4 (&raw)[4], bool ok, uint16_t* dst) -> bool {
+      if (quad) {
+        const uint32_t partner = rank ^ (X == 2u ? 2u : 1u);
+        if (!mbar_wait_cluster(bar(qbRecvFull + X), par, ctx, 59)) return false;
+        const uint32_t src = recv_base + X * kQRecvPart + row64 * 128u;
+#pragma unroll
+        for (uint32_t ch = 0; ch < 8u; ++ch) {
+          uint32_t w4[4];
+          lds128(src + ((ch ^ row_sw) << 4), w4);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            r[4 * ch + i] = __float_as_uint(__uint_as_float(r[4 * ch + i]) + __uint_as_float(w4[i]));
+        }
+        mbar_arrive_cluster(cluster_map(bar(qbRecvFree + X), partner));
+      }
+      float fmul = 1.f, cq = 0.f;
+      if (X != 0u) {
+        float ss = 0.f, qd = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint32_t w4[4] = {raw[ch].x, raw[ch].y, raw[ch].z, raw[ch].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x0 = Elem<T>::lo(w4[e]), x1 = Elem<T>::hi(w4[e]);
+            ss = fmaf(x0, x0, ss);
+            ss = fmaf(x1, x1, ss);
+            qd = fmaf(x0, __uint_as_float(r[8 * ch + 2 * e]), qd);
+            qd = fmaf(x1, __uint_as_float(r[8 * ch + 2 * e + 1]), qd);
+          }
+        }
+        const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+        const float dot = qd * rn;
+        if (X == 2u && ok) dscale_acc += dot;
+        fmul = scale * rn;
+        cq = rn * dot;
+      }
+      if (ok) {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint32_t w4[4] = {raw[ch].x, raw[ch].y, raw[ch].z, raw[ch].w};
+          uint32_t o4[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float v0 = __uint_as_float(r[8 * ch + 2 * e]), v1 = __uint_as_float(r[8 * ch + 2 * e + 1]);
+            if (X != 0u) {
+              v0 = fmul * (v0 - Elem<T>::lo(w4[e]) * cq);
+              v1 = fmul * (v1 - Elem<T>::hi(w4[e]) * cq);
+            }
+            o4[e] = Elem<T>::pack(v0, v1);
+          }
+          *reinterpret_cast<uint4*>(dst + 8 * ch) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+        }
+      }
+      return true;
+    };
+    // pushes first, so that no push ever waits behind a thread that waits for a push
+    if (quad) {
+      if (keeper) {
+        if (!push(rq, 2u)) return;
+      } else {
+        if (!push(rv, 0u)) return;
+        if (!push(rk, 1u)) return;
+      }
+    }
+    if (keeper) {
+      // (dV has no Jacobian: the raw row passed for it is not used)
+      if (!finish(rv, 0u, rawq, k_ok,
+                  static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + krow * p.dv_sn)) return;
+      if (!finish(rk, 1u, rawk, k_ok,
+                  static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + krow * p.dk_sn)) return;
+    }
+    if (fin_q) {
+      if (!finish(rq, 2u, rawq, q_ok,
+                  static_cast<uint16_t*>(p.dq) + bw * p.dq_sbw + g.h * p.dq_sh + qrow * p.dq_sn)) return;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// MMA issuer (one thread)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ void quad_mma_role(const QuadParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
+                              const WaitCtx& ctx, uint32_t rank) {
+  const QuadGeom g = quad_geom(p, rank);
+  if (g.count == 0) return;
+  constexpr uint32_t fmt = Elem<T>::kFmt;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const uint32_t idesc_s = make_idesc(fmt, 128, kStepCols, 0, 0);
+  const uint32_t idesc_acc = make_idesc(fmt, 128, 32, 0, 1);   // A in TMEM, B MN-major
+  const uint32_t idesc_dq = make_idesc(fmt, 128, 32, 1, 1);    // A and B MN-major
+  const DescBase dk64 = make_desc_base(0, 16, 512, kSw64);      // K-major rows of 64 bytes
+  const DescBase dm64 = make_desc_base(0, 512, 512, kSw64);     // MN-major rows of 64 bytes
+  const DescBase dds = make_desc_base(0, 16384, 1024, kSw128);  // dS tile, MN-major, two slabs
+  const bool with_db = p.db_partial != nullptr;
+  const uint32_t ident = smem_base + p.off_ident;
+  const uint32_t ds_base = smem_base + p.off_ds;
+
+  // S^T = K^ Q^^T and dP^T = V dO^T for the 64 queries of step w
+  auto issue_sdp = [&](uint32_t w, uint32_t stage_base) {
+    const uint32_t row_off = w * (kStepCols * kRowBytes);
+    const uint32_t st_ = tmem + w * 128u + kQTmS, dpt = tmem + w * 128u + kQTmDP;
+#pragma unroll
+    for (uint32_t k = 0; k < 2u; ++k) {
+      mma_ss(st_, desc_at(dk64, stage_base + 32u * k), desc_at(dk64, stage_base + 16384u + row_off + 32u * k),
+             idesc_s, k);
+      mma_ss(dpt, desc_at(dk64, stage_base + 8192u + 32u * k),
+             desc_at(dk64, stage_base + 24576u + row_off + 32u * k), idesc_s, k);
+    }
+    mma_commit(bar(qbSFull + static_cast<int>(w)));
+  };
+
+  Ring st(p.n_stages);
+  if (!mbar_wait(bar(qbReady + 0), 0u, ctx, 60)) return;
+  tc_fence_after();
+#pragma unroll 1
+  for (uint32_t w = 0; w < 2u; ++w) issue_sdp(w, smem_base + p.off_stage);
+
+#pragma unroll 1
+  for (int n = 0; n < g.count; ++n) {
+    const uint32_t par = static_cast<uint32_t>(n) & 1u;
+    const uint32_t base = smem_base + p.off_stage + st.stage * kQStageBytes;
+    const bool has_next = n + 1 < g.count;
+    Ring nx = st;
+    nx.advance();
+    // the accumulators of the previous job have been read out
+    if (n > 0) {
+      if (!mbar_wait(bar(qbAccFree), par ^ 1u, ctx, 62)) return;
+    }
+#pragma unroll 1
+    for (uint32_t w = 0; w < 2u; ++w) {
+      if (!mbar_wait(bar(qbPReady + static_cast<int>(w)), par, ctx, 64)) return;
+      tc_fence_after();
+#pragma unroll 1
+      for (uint32_t c = 0; c < 2u; ++c) {
+        const uint32_t row_off = (w * kStepCols + c * kChunkCols) * kRowBytes;
+        const uint32_t a_p = tmem + w * 128u + kQTmS + 32u * c, a_ds = tmem + w * 128u + kQTmDP + 32u * c;
+#pragma unroll
+        for (uint32_t k = 0; k < 2u; ++k) {
+          const uint32_t acc = (w | c | k) ? 1u : 0u;
+          mma_ts(tmem + kQTmDV, a_p + k * 8u, desc_at(dm64, base + 24576u + row_off + k * 1024u), idesc_acc, acc);
+          mma_ts(tmem + kQTmDK, a_ds + k * 8u, desc_at(dm64, base + 16384u + row_off + k * 1024u), idesc_acc, acc);
+          // dB^T += dS^T I: the tensor core sums over the windows of this cluster (each step has
+          // its own copy of the identity tile)
+          if (with_db)
+            mma_ts(tmem + kQTmDB + 64u * w + 32u * c, a_ds + k * 8u, desc_at(dm64, ident + 2048u * w + k * 1024u),
+                   idesc_acc, 1u);
+        }
+      }
+      // the next job's scores of step w go over this job's P^T / dS^T of the step (the tensor
+      // core works in issue order), so that warpgroup w can go on while the rest is issued
+      if (has_next) {
+        if (w == 0u) {
+          if (!mbar_wait(bar(qbReady + nx.stage), nx.phase, ctx, 66)) return;
+          tc_fence_after();
+        }
+        issue_sdp(w, smem_base + p.off_stage + nx.stage * kQStageBytes);
+      }
+    }
+    // dQ^ = dS K^ over the 128 keys of the block
+#pragma unroll 2
+    for (uint32_t k = 0; k < 8u; ++k)
+      mma_ss(tmem + kQTmDQ, desc_at(dds, ds_base + k * 2048u), desc_at(dm64, base + k * 1024u), idesc_dq, k);
+    mma_commit(bar(qbAccFull));
+    mma_commit(bar(qbDsFree));
+    // (the next job's scores, issued above, read only the next stage)
+    mma_commit(bar(qbFree + st.stage));
+    st = nx;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// TMA producer (one thread): the bias tile once, then per job the four row tiles and the mask tile
+// ------------------------------------------------------------------------------------------------
+__device__ void quad_load_role(const QuadParams& p, uint32_t smem_base, uint32_t bars, const WaitCtx& ctx,
+                               uint32_t rank) {
+  const QuadGeom g = quad_geom(p, rank);
+  if (g.count == 0) return;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  const int k0 = static_cast<int>(g.a) * kTileRows, q0 = static_cast<int>(g.b) * kTileRows;
+  auto load_table = [&](uint32_t dst, const CUtensorMap* map, uint32_t full, int plane) {
+    mbar_arrive_expect_tx(full, kQTableBytes);
+#pragma unroll 1
+    for (int ci = 0; ci < 4; ++ci) {
+#pragma unroll 1
+      for (int hb = 0; hb < 2; ++hb)
+        tma_load_3d(dst + ci * kTableTileBytes + hb * kBoxBytes, map, full, q0 + ci * kChunkCols,
+                    k0 + hb * kBoxRows, plane);
+    }
+  };
+  if (p.has_bias) load_table(smem_base + p.off_bias, &p.tm_biasT, bar(qbBiasFull), g.h);
+  Ring st(p.n_stages), mk(p.n_mask_stages);
+#pragma unroll 1
+  for (int n = 0; n < g.count; ++n) {
+    const int bw = g.slot + n * p.nslots;
+    if (!mbar_wait<true>(bar(qbFree + st.stage), st.phase ^ 1u, ctx, 70)) return;
+    const uint32_t base = smem_base + p.off_stage + st.stage * kQStageBytes;
+    const uint32_t full = bar(qbFull + st.stage);
+    mbar_arrive_expect_tx(full, kQStageBytes);
+#pragma unroll 1
+    for (int hb = 0; hb < 2; ++hb) {
+      tma_load_4d(base + hb * kBoxBytes, &p.tm_k, full, 0, k0 + hb * kBoxRows, g.h, bw);
+      tma_load_4d(base + 16384u + hb * kBoxBytes, &p.tm_q, full, 0, q0 + hb * kBoxRows, g.h, bw);
+      tma_load_4d(base + 8192u + hb * kBoxBytes, &p.tm_v, full, 0, k0 + hb * kBoxRows, g.h, bw);
+      tma_load_4d(base + 24576u + hb * kBoxBytes, &p.tm_do, full, 0, q0 + hb * kBoxRows, g.h, bw);
+    }
+    st.advance();
+    if (p.has_mask) {
+      if (!mbar_wait<true>(bar(qbMaskFree + mk.stage), mk.phase ^ 1u, ctx, 72)) return;
+      load_table(smem_base + p.off_mask + mk.stage * kQTableBytes, &p.tm_maskT, bar(qbMaskFull + mk.stage),
+                 bw % p.nW);
+      mk.advance();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_constant__ QuadParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t tid = threadIdx.x;
+  const uint32_t warp = tid >> 5;
+  const uint32_t lane = tid & 31u;
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const uint32_t bars = smem_base + p.off_ctrl;
+  uint32_t* ctrl_words = reinterpret_cast<uint32_t*>(smem_raw + p.off_ctrl + 8u * kQuadNumBars);
+  uint32_t& tmem_slot = ctrl_words[0];
+  float* warp_sums = reinterpret_cast<float*>(&ctrl_words[4]);
+  const bool clustered = p.cluster > 1;
+  const uint32_t rank = clustered ? cluster_ctarank() : 0u;
+  // (a misaligned dynamic shared-memory base would be the same in every CTA of the launch, so
+  // leaving here cannot strand a partner in the cluster)
+  if ((smem_base & 1023u) != 0u) {
+    if (tid == 0 && p.status != nullptr) atomicCAS(&p.status->code, 0u, (99u << 8) | 2u);
+    return;
+  }
+
+  if (tid == 0) {
+    ctrl_words[1] = 0u;
+    for (int i = 0; i < kQuadNumBars; ++i) {
+      uint32_t count = 1u;
+      if (i >= qbReady && i < qbFree) count = 128u;            // the preparing warpgroup
+      else if (i >= qbMaskFree && i < qbBiasFull) count = 256u;
+      else if (i >= qbPReady && i < qbAccFull) count = 128u;
+      else if (i == qbAccFree) count = 128u;                   // the epilogue warpgroup
+      else if (i >= qbRecvFull && i < qbDsFree) count = 64u;
+      mbar_init(bars + 8u * i, count);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&p.tm_q);
+    tma_prefetch_desc(&p.tm_k);
+    tma_prefetch_desc(&p.tm_v);
+    tma_prefetch_desc(&p.tm_do);
+    if (p.has_bias) tma_prefetch_desc(&p.tm_biasT);
+    if (p.has_mask) tma_prefetch_desc(&p.tm_maskT);
+  }
+  if (warp == 16) {
+    tmem_alloc(smem_u32(&tmem_slot), kQuadTmemCols);
+    tmem_relinquish();
+  }
+  // 32 x 32 identity in the layout of a dO chunk (row = query, 64 bytes of columns, 16-byte pieces
+  // XOR-swizzled with the row), two copies: B operand of the products that sum dS^T into dB^T
+  for (uint32_t wj = tid; wj < 1024u; wj += kQuadThreads) {
+    const uint32_t wi = wj & 511u;
+    const uint32_t row = wi >> 4, piece = (wi >> 2) & 3u, word = wi & 3u;   // word = two columns
+    const uint32_t col = ((piece ^ ((row >> 1) & 3u)) << 3) + 2u * word;     // logical column of the low half
+    const uint32_t one = Elem<T>::pack(1.f, 0.f) & 0xFFFFu;
+    uint32_t v = 0u;
+    if (col == row) v = one;
+    if (col + 1u == row) v = one << 16;
+    reinterpret_cast<uint32_t*>(smem_raw + p.off_ident)[wj] = v;
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // every CTA of the cluster has initialised its barriers before anyone arrives on a peer's
+  if (clustered) cluster_sync_all();
+  const uint32_t tmem = tmem_slot;
+  WaitCtx ctx{&ctrl_words[1], p.status, p.prof};
+#if FWA2_TRACE
+  const long long prof_t0 = clock64();
+#endif
+
+  float dscale_acc = 0.f;
+  // 640 threads start with 96 registers each.  setmaxnreg only moves registers inside what the
+  // CTA was given at launch (an increase beyond it would wait for ever), so the four budgets
+  // below must not add up to more than 640 x 96.
+  constexpr uint32_t kRegCompute = 120, kRegEpilogue = 144, kRegPrepare = 48, kRegIssue = 48;
+  static_assert(2 * 128 * kRegCompute + 128 * (kRegEpilogue + kRegPrepare + kRegIssue) <= kQuadThreads * 96,
+                "register budgets exceed the launch allocation");
+  if (warp < 8) {
+    reg_alloc<kRegCompute>();
+    quad_compute_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, rank);
+  } else if (warp < 12) {
+    reg_alloc<kRegEpilogue>();
+    quad_epilogue_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, rank, dscale_acc);
+  } else if (warp < 16) {
+    reg_dealloc<kRegPrepare>();
+    quad_prepare_role<T>(p, smem_raw, smem_base, bars, ctx, rank);
+  } else {
+    reg_dealloc<kRegIssue>();
+    if (lane == 0) {
+      if (warp == 16) quad_mma_role<T>(p, smem_base, bars, tmem, ctx, rank);
+      else if (warp == 17) quad_load_role(p, smem_base, bars, ctx, rank);
+    }
+  }
+  __syncwarp();
+  // deterministic CTA-wide sum of the dLogitScale contributions
+  if (warp >= 8 && warp < 12) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dscale_acc += __shfl_xor_sync(0xFFFFFFFFu, dscale_acc, off);
+    if (lane == 0) warp_sums[warp - 8] = dscale_acc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && p.dscale_partial != nullptr) {
+    const int cid = static_cast<int>(blockIdx.x) / p.cluster;
+    const int h = cid % p.H, slot = cid / p.H;
+    float s = 0.f;
+    for (int w = 0; w < 4; ++w) s += warp_sums[w];
+    p.dscale_partial[(slot * p.cluster + static_cast<int>(rank)) * p.H + h] =
+        s * load_scale<T>(p.scale, p.scale_is_tensor, h);
+  }
+#if FWA2_TRACE
+  if (tid == 0 && blockIdx.x == 0 && p.prof != nullptr) {
+    p.prof[0] = static_cast<unsigned long long>(clock64() - prof_t0);
+    p.prof[1] = static_cast<unsigned long long>(quad_geom(p, rank).count);
+  }
+#endif
+  if (tid == 0) report_abort(ctrl_words[1], p.status);
+  if (ctrl_words[1]) {
+    __nanosleep(20000);
+    __syncthreads();
+  }
+  // nobody leaves (and frees its shared memory) while a peer may still push rows or arrive here
+  if (clustered) cluster_sync_all();
+  if (warp == 16) tmem_dealloc(tmem, kQuadTmemCols);
+}
+
+template __global__ void bwd_quad_kernel<__nv_bfloat16>(const __grid_constant__ QuadParams);
+template __global__ void bwd_quad_kernel<__half>(const __grid_constant__ QuadParams);
+
+namespace {
+template <typename K>
+cudaError_t quad_config(K kern, const QuadParams& p, int grid, cudaStream_t stream, cudaLaunchConfig_t* cfg,
+                        cudaLaunchAttribute* attr) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(p.smem_bytes));
+  if (e != cudaSuccess) return e;
+  cfg->gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg->blockDim = dim3(kQuadThreads, 1, 1);
+  cfg->dynamicSmemBytes = p.smem_bytes;
+  cfg->stream = stream;
+  attr->id = cudaLaunchAttributeClusterDimension;
+  attr->val.clusterDim.x = static_cast<unsigned>(p.cluster);
+  attr->val.clusterDim.y = 1;
+  attr->val.clusterDim.z = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+  return cudaSuccess;
+}
+}  // namespace
+
+// How many clusters of `cluster` CTAs with `smem_bytes` of shared memory the current device can
+// hold at once (0 on error).
+int quad_max_active_clusters(int dtype_is_bf16, int cluster, uint32_t smem_bytes) {
+  QuadParams p{};
+  p.cluster = cluster;
+  p.smem_bytes = smem_bytes;
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr{};
+  int n = 0;
+  cudaError_t e;
+  if (dtype_is_bf16) {
+    e = quad_config(bwd_quad_kernel<__nv_bfloat16>, p, cluster, nullptr, &cfg, &attr);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, bwd_quad_kernel<__nv_bfloat16>, &cfg);
+  } else {
+    e = quad_config(bwd_quad_kernel<__half>, p, cluster, nullptr, &cfg, &attr);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, bwd_quad_kernel<__half>, &cfg);
+  }
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+cudaError_t launch_bwd_quad(const QuadParams& p, int dtype_is_bf16, int grid, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr{};
+  cudaError_t e;
+  if (dtype_is_bf16) {
+    e = quad_config(bwd_quad_kernel<__nv_bfloat16>, p, grid, stream, &cfg, &attr);
+    if (e != cudaSuccess) return e;
+    e = cudaLaunchKernelEx(&cfg, bwd_quad_kernel<__nv_bfloat16>, p);
+  } else {
+    e = quad_config(bwd_quad_kernel<__half>, p, grid, stream, &cfg, &attr);
+    if (e != cudaSuccess) return e;
+    e = cudaLaunchKernelEx(&cfg, bwd_quad_kernel<__half>, p);
+  }
+  if (e != cudaSuccess) return e;
+  return cudaGetLastError();
+}
+
+}  // namespace fwa2

@@ -193,6 +193,46 @@ struct BwdParams {
   Trace trace;
 };
 
+// Backward for windows of 65 to 256 tokens ("quad" kernel).  The N x N score matrix of a unit is
+// cut into 128 x 128 tiles (key block a, query tile b); a cluster of `cluster` CTAs (4, or 1 for
+// windows of at most 128 tokens) works on one unit at a time, CTA rank 2 a + b on tile (a, b).
+// Cluster c works on head (c mod H) only, on the windows slot, slot + nslots, ... (slot = c / H),
+// so each CTA keeps its tile of the window-summed dBias in tensor memory for the whole kernel.
+struct QuadParams {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do;   // 4-D (d, N, H, BW), box (32, 64, 1, 1)
+  CUtensorMap tm_biasT, tm_maskT;        // 3-D transposed tables (N_pad, N, planes), box (32, 64, 1)
+  const void* q;  long long q_sbw, q_sh, q_sn;
+  const void* k;  long long k_sbw, k_sh, k_sn;
+  const void* o;  long long o_sbw, o_sh, o_sn;
+  void* dq;       long long dq_sbw, dq_sh, dq_sn;
+  void* dk;       long long dk_sbw, dk_sh, dk_sn;
+  void* dv;       long long dv_sbw, dv_sh, dv_sn;
+  const float* lse;
+  long long lse_sbw, lse_sh;
+  const void* scale;
+  int scale_is_tensor;
+  float* db_partial;          // [clusters][db_pitch][db_pitch] fp32: (query, key); nullptr = no dBias
+  long long db_buf_stride;
+  int db_pitch;
+  float* dscale_partial;      // [(slot * cluster + rank) * H + h]
+  int BW, H, N, nW;
+  int has_bias, has_mask;
+  int cluster;                // CTAs per cluster: 1 or 4
+  int nslots;                 // clusters = nslots * H
+  int n_stages, n_mask_stages;
+  uint32_t off_stage;         // n_stages x [K | V | Q | dO], 8 KiB each
+  uint32_t off_mask;          // n_mask_stages x four chunks of (128 keys x 32 queries) mask^T
+  uint32_t off_bias;          // the same four chunks of bias^T, loaded once
+  uint32_t off_ds;            // dS tile, 32 KiB (two slabs of 64 queries)
+  uint32_t off_recv;          // three partial accumulators of 64 rows x 32 fp32 pushed by peers
+  uint32_t off_ident;         // two 32 x 32 identity tiles
+  uint32_t off_rowstats;      // n_stages x (128 lse*log2e, 128 delta) floats
+  uint32_t off_ctrl;
+  uint32_t smem_bytes;
+  DeviceStatus* status;
+  unsigned long long* prof;   // development builds (-DFWA2_TRACE=1): cycles waited per site, CTA 0
+};
+
 // Second stage of the dBias / dLogitScale reduction.
 struct ReduceParams {
   const float* db_partial;     // [n_bufs][pitch][pitch] (query, key)
@@ -200,6 +240,7 @@ struct ReduceParams {
   int pitch;
   const float* dscale_partial; // [grid]
   int H, N, BW, nslots, pair;
+  int dscale_slots;            // dLogitScale partials per head (laid out [slot][H])
   float* out_f32;              // (H*N*N + H) or nullptr
   void* dbias;                 // (H, N, N) output dtype or nullptr
   void* dscale;                // H values or nullptr

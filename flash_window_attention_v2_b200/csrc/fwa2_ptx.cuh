@@ -126,7 +126,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     for (long long it = 0; it < (1ll << 26) && !done; ++it) done = mbar_try_wait(bar, parity);
     const uint32_t warp = threadIdx.x >> 5;
     if (ctx.wait_acc != nullptr && blockIdx.x == 0 && (threadIdx.x & 31u) == 0u &&
-        (warp == 0u || warp == 4u || (warp >= 8u && warp <= 12u)))
+        (warp == 0u || warp == 4u || warp == 8u || warp == 12u || warp == 16u))
       atomicAdd(ctx.wait_acc + site + (warp == 4u ? 100u : 0u), static_cast<unsigned long long>(clock64() - w0));
     return done;
   }
@@ -163,6 +163,78 @@ __device__ __forceinline__ void report_abort(uint32_t abort_word, DeviceStatus* 
     if (atomicCAS(&status->code, 0u, code) == 0u) {
       status->block = blockIdx.x;
       status->detail = 0u;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Thread-block clusters: the rank of this CTA, a peer CTA's view of one of my shared-memory
+// addresses, plain stores into a peer's shared memory, and mbarrier traffic with cluster scope
+// (a peer's stores followed by its release-arrive are visible after an acquire-wait).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, const uint32_t* v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(v[0]),
+               "r"(v[1]), "r"(v[2]), "r"(v[3])
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait for a phase that a peer CTA of the cluster completes.  Same contract as
+// mbar_wait(): false once the wait was abandoned (the CTA's abort word then names the site).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                                  uint32_t site) {
+#if defined(FWA2_TRACE) && FWA2_TRACE
+  {
+    const long long w0 = clock64();
+    bool done = false;
+    for (long long it = 0; it < (1ll << 26) && !done; ++it) done = mbar_try_wait_cluster(bar, parity);
+    const uint32_t warp = threadIdx.x >> 5;
+    if (ctx.wait_acc != nullptr && blockIdx.x == 0 && (threadIdx.x & 31u) == 0u &&
+        (warp == 0u || warp == 4u || warp == 8u || warp == 12u || warp == 16u))
+      atomicAdd(ctx.wait_acc + site + (warp == 4u ? 100u : 0u), static_cast<unsigned long long>(clock64() - w0));
+    return done;
+  }
+#endif
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint32_t t0 = static_cast<uint32_t>(clock());
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++spins & 0xFFu) == 0) {
+      if (*ctx.abort_flag) return false;
+      if (static_cast<uint32_t>(clock()) - t0 > static_cast<uint32_t>(kWaitLimitCycles)) {
+        *ctx.abort_flag = (site << 8) | kStatusTimeout;
+        return false;
+      }
     }
   }
 }
@@ -251,6 +323,17 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                : "r"(taddr)
                : "memory");
 }
+// 32 lanes x 16 columns.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
                "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
@@ -307,8 +390,10 @@ __device__ __forceinline__ DescBase make_desc_base(uint32_t smem_addr, uint32_t 
   const uint64_t d = make_smem_desc(smem_addr, lbo_bytes, sbo_bytes, sw);
   return DescBase{static_cast<uint32_t>(d), static_cast<uint32_t>(d >> 32)};
 }
+// (Inside a thread-block cluster the shared-memory address of a CTA other than rank 0 carries the
+// rank above bit 24; only the offset inside the CTA's own window belongs in the descriptor.)
 __device__ __forceinline__ uint64_t desc_at(const DescBase& b, uint32_t byte_offset) {
-  return (static_cast<uint64_t>(b.hi) << 32) | static_cast<uint64_t>(b.lo + (byte_offset >> 4));
+  return (static_cast<uint64_t>(b.hi) << 32) | static_cast<uint64_t>(b.lo + ((byte_offset & 0x3FFFFu) >> 4));
 }
 
 // Position in a ring of `n` pipeline stages with the mbarrier phase bit that goes with it.

@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(32 * kReduceLanes) reduce_partials_kernel(cons
   // list was the longest dependency chain of this kernel)
   if (blockIdx.x == 0 && blockIdx.y == 0 && ty == 0 && p.dscale_partial != nullptr) {
     float s = 0.f;
-    for (int sl = tx; sl < p.nslots; sl += 32) s += p.dscale_partial[sl * p.H + h];
+    for (int sl = tx; sl < p.dscale_slots; sl += 32) s += p.dscale_partial[sl * p.H + h];
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
     if (tx != 0) {

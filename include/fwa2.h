@@ -47,6 +47,9 @@ enum fwa2_error {
 #define FWA2_BWD_SKIP_REDUCE 4   /* backward: leave the per-CTA partials in the workspace */
 #define FWA2_BWD_SKIP_DBIAS 8    /* backward, timing experiments only: do not accumulate dBias
                                     (dbias then holds garbage) */
+#define FWA2_BWD_GENERAL_KERNEL 16 /* backward: windows of 65 to 256 tokens normally run on the
+                                    cluster kernel (one 128 x 128 score tile per CTA); this bit
+                                    selects the general kernel for them instead */
 
 /* A (BW, H, N, 32) tensor of 16-bit elements with unit stride along the last axis.
  * Strides are in elements. */
