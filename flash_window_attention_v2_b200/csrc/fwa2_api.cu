@@ -176,10 +176,10 @@ BwdPlan make_bwd_plan(int bw, int heads, int n, int n_windows, bool has_bias, bo
 
 // Shared-memory layout of the cluster kernel; false if it does not fit.
 bool quad_smem_plan(QuadParams& p, uint32_t budget) {
-  const uint32_t mask_b = p.has_mask ? 2u * 32768u : 0u, bias_b = p.has_bias ? 32768u : 0u;
+  const uint32_t mask_b = p.has_mask ? 2u * 32768u : 0u;
   const uint32_t recv_b = p.cluster > 1 ? 3u * 64u * 128u : 0u;
   auto total = [&](uint32_t ns) {
-    return ns * 32768u + mask_b + bias_b + 32768u + recv_b + 4096u + ns * 1024u + kCtrlBytes;
+    return ns * 32768u + mask_b + 32768u + recv_b + 4096u + ns * 1024u + kCtrlBytes;
   };
   uint32_t ns = 3;
   if (total(ns) > budget) ns = 2;
@@ -188,8 +188,7 @@ bool quad_smem_plan(QuadParams& p, uint32_t budget) {
   p.n_mask_stages = 2;
   p.off_stage = 0;
   p.off_mask = p.off_stage + ns * 32768u;
-  p.off_bias = p.off_mask + mask_b;
-  p.off_ds = p.off_bias + bias_b;
+  p.off_ds = p.off_mask + mask_b;
   p.off_recv = p.off_ds + 32768u;
   p.off_ident = p.off_recv + recv_b;
   p.off_rowstats = p.off_ident + 4096u;
@@ -383,9 +382,8 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
     if ((rc = encode_rows4(&qp.tm_k, a->k, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
     if ((rc = encode_rows4(&qp.tm_v, a->v, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
     if ((rc = encode_rows4(&qp.tm_do, a->dout, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
-    if (has_bias &&
-        (rc = encode_table3(&qp.tm_biasT, bias_t, a->dtype, a->heads, a->n, a->n, pl.table_pitch)) != FWA2_OK)
-      return rc;
+    qp.bias_t = has_bias ? bias_t : nullptr;
+    qp.table_pitch = pl.table_pitch;
     if (has_mask &&
         (rc = encode_table3(&qp.tm_maskT, mask_t, a->dtype, a->n_windows, a->n, a->n, pl.table_pitch)) != FWA2_OK)
       return rc;

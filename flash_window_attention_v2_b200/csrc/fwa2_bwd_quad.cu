@@ -30,6 +30,8 @@
 
 #include <cuda_runtime.h>
 
+#include <type_traits>
+
 namespace fwa2 {
 
 constexpr int kQuadThreads = 640;
@@ -49,8 +51,8 @@ enum QuadBar : int {
   qbSFull = 14, qbPReady = 16,                // per step
   qbAccFull = 18, qbAccFree = 19,
   qbRecvFull = 20, qbRecvFree = 23,           // per pushed accumulator: 0 dV, 1 dK, 2 dQ
-  qbDsFree = 26,
-  kQuadNumBars = 27
+  qbDsFree = 26, qbAccFreeQ = 27,
+  kQuadNumBars = 28
 };
 
 struct QuadGeom {
@@ -69,6 +71,44 @@ __device__ __forceinline__ QuadGeom quad_geom(const QuadParams& p, uint32_t rank
   return g;
 }
 
+// Bounded wait, written to be small: it is inlined at sixteen sites of a kernel whose roles must
+// share a 32 KiB instruction cache.  kCluster: the phase is completed by a peer CTA (acquire at
+// cluster scope).  Returns false once the wait was abandoned; the CTA's abort word then holds
+// (site << 8 | kind).  The clock and the abort word are looked at every 4096 polls.
+template <bool kCluster = false>
+__device__ __forceinline__ bool qwait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, uint32_t site) {
+#if FWA2_TRACE
+  return kCluster ? mbar_wait_cluster(bar, parity, ctx, site) : mbar_wait(bar, parity, ctx, site);
+#else
+  uint32_t spins = 0, t0 = 0;
+  while (!(kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))) {
+    if ((++spins & 0xFFFu) == 0u) {
+      const uint32_t now = static_cast<uint32_t>(clock());
+      if (spins == 0x1000u) t0 = now;
+      if (*ctx.abort_flag != 0u || now - t0 > static_cast<uint32_t>(kWaitLimitCycles)) {
+        if (*ctx.abort_flag == 0u) *ctx.abort_flag = (site << 8) | kStatusTimeout;
+        return false;
+      }
+    }
+  }
+  return true;
+#endif
+}
+
+#if FWA2_TRACE
+#define QPROF_BEGIN() long long qprof_t = clock64()
+#define QPROF_SEG(idx)                                                                              \
+  do {                                                                                              \
+    const long long qprof_n = clock64();                                                            \
+    if (p.prof != nullptr && blockIdx.x == 0 && (threadIdx.x & 31u) == 0u && ((threadIdx.x >> 5) & 3u) == 0u) \
+      atomicAdd(p.prof + 200 + (idx), static_cast<unsigned long long>(qprof_n - qprof_t));        \
+    qprof_t = qprof_n;                                                                              \
+  } while (0)
+#else
+#define QPROF_BEGIN() do {} while (0)
+#define QPROF_SEG(idx) do {} while (0)
+#endif
+
 __device__ __forceinline__ uint4 quad_ldg_v4(const void* ptr) {
   uint4 v;
   asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -85,31 +125,41 @@ __device__ __forceinline__ uint4 quad_ldg_v4(const void* ptr) {
 // finite; a query past the end has lse2 = +inf, hence p = ds = 0; a key past the end only feeds
 // rows of dK / dV / dB that are never stored, and its row of K^ is zero in the dQ product.
 // ------------------------------------------------------------------------------------------------
+// Sixteen queries at a time, two per instruction where the hardware has paired fp32 forms
+// (fma / add / mul .f32x2).  nl2 = -lse * log2(e) and nd = -delta come from shared memory with
+// their signs already flipped, so that both subtractions are additions.
 template <typename T>
-__device__ __forceinline__ void quad_group(bool has_bias, bool has_mask, const uint32_t (&sv)[8],
-                                           const uint32_t (&dpv)[8], uint32_t bias_addr,
-                                           uint32_t mask_addr, const float* lse2, const float* delta,
-                                           float scale, uint32_t (&pw)[4], uint32_t (&dw)[4]) {
-  uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
-  if (has_bias) lds128(bias_addr, wb);
-  if (has_mask) lds128(mask_addr, wm);
-  const float4 la = *reinterpret_cast<const float4*>(lse2);
-  const float4 lb = *reinterpret_cast<const float4*>(lse2 + 4);
-  const float4 da = *reinterpret_cast<const float4*>(delta);
-  const float4 db = *reinterpret_cast<const float4*>(delta + 4);
-  const float l8[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-  const float d8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+__device__ __forceinline__ void quad_half(const uint32_t (&sv)[16], const uint32_t (&dpv)[16],
+                                          const uint32_t* wb /* 8 words */, bool has_mask, uint32_t mask_addr0,
+                                          uint32_t mask_addr1, const float* nl2, const float* nd, float scale,
+                                          uint32_t (&pw)[8], uint32_t (&dw)[8]) {
+  uint32_t wm[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+  if (has_mask) {
+    lds128(mask_addr0, reinterpret_cast<uint32_t(&)[4]>(wm[0]));
+    lds128(mask_addr1, reinterpret_cast<uint32_t(&)[4]>(wm[4]));
+  }
+  const float2 scale2 = make_float2(scale, scale), log2e2 = make_float2(kLog2e, kLog2e);
 #pragma unroll
-  for (int e2 = 0; e2 < 4; ++e2) {
-    const int e = 2 * e2;
-    const float x0 = fmaf(__uint_as_float(sv[e]), scale, Elem<T>::lo(wb[e2])) + Elem<T>::lo(wm[e2]);
-    const float x1 = fmaf(__uint_as_float(sv[e + 1]), scale, Elem<T>::hi(wb[e2])) + Elem<T>::hi(wm[e2]);
-    const float p0 = ex2f(fmaf(x0, kLog2e, -l8[e]));
-    const float p1 = ex2f(fmaf(x1, kLog2e, -l8[e + 1]));
-    const float s0 = p0 * (__uint_as_float(dpv[e]) - d8[e]);
-    const float s1 = p1 * (__uint_as_float(dpv[e + 1]) - d8[e + 1]);
-    pw[e2] = Elem<T>::pack(p0, p1);
-    dw[e2] = Elem<T>::pack(s0, s1);
+  for (int g4 = 0; g4 < 4; ++g4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(nl2 + 4 * g4);
+    const float4 d4 = *reinterpret_cast<const float4*>(nd + 4 * g4);
+#pragma unroll
+    for (int hp = 0; hp < 2; ++hp) {
+      const int e2 = 2 * g4 + hp, e = 2 * e2;
+      const float2 s2 = make_float2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1]));
+      const float2 b2 = make_float2(Elem<T>::lo(wb[e2]), Elem<T>::hi(wb[e2]));
+      const float2 m2 = make_float2(Elem<T>::lo(wm[e2]), Elem<T>::hi(wm[e2]));
+      const float2 l2 = hp == 0 ? make_float2(l4.x, l4.y) : make_float2(l4.z, l4.w);
+      const float2 n2 = hp == 0 ? make_float2(d4.x, d4.y) : make_float2(d4.z, d4.w);
+      float2 x2 = __ffma2_rn(s2, scale2, b2);
+      if (has_mask) x2 = __fadd2_rn(x2, m2);
+      const float2 y2 = __ffma2_rn(x2, log2e2, l2);
+      const float2 p2 = make_float2(ex2f(y2.x), ex2f(y2.y));
+      const float2 t2 = __fadd2_rn(make_float2(__uint_as_float(dpv[e]), __uint_as_float(dpv[e + 1])), n2);
+      const float2 ds2 = __fmul2_rn(p2, t2);
+      pw[e2] = Elem<T>::pack(p2.x, p2.y);
+      dw[e2] = Elem<T>::pack(ds2.x, ds2.y);
+    }
   }
 }
 
@@ -133,6 +183,28 @@ __device__ void quad_compute_role(const QuadParams& p, uint8_t* smem_ptr, uint32
   const uint32_t tm_s = tmem + lane_base + wg * 128u + kQTmS;
   const uint32_t tm_d = tmem + lane_base + wg * 128u + kQTmDP;
 
+  // This thread meets the same 64 bias entries in every job (its key, the 64 queries of its step,
+  // the cluster's head): they live in registers for the whole kernel, as 32 packed pairs, read
+  // once from the transposed table.
+  uint32_t wb[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) wb[i] = 0u;
+  if (p.has_bias) {
+    const int key = static_cast<int>(g.a * kTileRows + lt);
+    const int q0 = static_cast<int>(g.b * kTileRows + wg * kStepCols);
+    if (key < p.N) {
+      const uint16_t* src = static_cast<const uint16_t*>(p.bias_t) +
+                            (static_cast<long long>(g.h) * p.N + key) * p.table_pitch + q0;
+#pragma unroll
+      for (int pc = 0; pc < 8; ++pc) {
+        if (q0 + 8 * pc < p.table_pitch) {
+          const uint4 v = quad_ldg_v4(src + 8 * pc);
+          wb[4 * pc] = v.x; wb[4 * pc + 1] = v.y; wb[4 * pc + 2] = v.z; wb[4 * pc + 3] = v.w;
+        }
+      }
+    }
+  }
+
   if (p.db_partial != nullptr) {
     // the dB^T sums of my step's 64 query columns start from zero (the first product that adds to
     // them is issued after this warpgroup's first P^T barrier)
@@ -149,58 +221,56 @@ __device__ void quad_compute_role(const QuadParams& p, uint8_t* smem_ptr, uint32
 #pragma unroll 1
   for (int n = 0; n < g.count; ++n) {
     const uint32_t par = static_cast<uint32_t>(n) & 1u;
-    if (!mbar_wait(bar(qbReady + st.stage), st.phase, ctx, 51)) return;     // row statistics
-    if (n == 0 && p.has_bias) {
-      if (!mbar_wait(bar(qbBiasFull), 0u, ctx, 57)) return;
-    }
+    if (!qwait(bar(qbReady + st.stage), st.phase, ctx, 51)) return;     // row statistics
     if (p.has_mask) {
-      if (!mbar_wait(bar(qbMaskFull + mk.stage), mk.phase, ctx, 54)) return;
+      if (!qwait(bar(qbMaskFull + mk.stage), mk.phase, ctx, 54)) return;
     }
-    if (!mbar_wait(bar(qbSFull + wg), par, ctx, 52)) return;
+    if (!qwait(bar(qbSFull + wg), par, ctx, 52)) return;
     tc_fence_after();
+    QPROF_BEGIN();
     {
-      const float* lse2 = rowstats + st.stage * 256u + wg * 64u;
-      const float* delta = rowstats + st.stage * 256u + 128u + wg * 64u;
-      // eight groups of eight queries (two table chunks of 32); the scores of the next group are
-      // fetched from tensor memory while the current one is computed
-      uint32_t sa[8], da[8], sb[8], db8[8];
-      tmem_ld8(tm_s, sa);
-      tmem_ld8(tm_d, da);
-      tmem_wait_ld();
+      const float* nl2 = rowstats + st.stage * 256u + wg * 64u;
+      const float* nd = rowstats + st.stage * 256u + 128u + wg * 64u;
+      const uint32_t mask_row = smem_base + p.off_mask + mk.stage * kQTableBytes + tab_row;
+      // Two trips of 32 queries (one table chunk each), each written out as two pieces of
+      // sixteen.  The trip is rolled to keep the code small (all roles of the kernel have to fit
+      // the instruction cache together); its sixteen bias words are picked out of the 32 the
+      // thread holds with one select each.
 #pragma unroll 1
-      for (uint32_t gi = 0; gi < 8u; ++gi) {
-        const uint32_t c = gi >> 2, gq = gi & 3u;
-        uint32_t pw[4], dw[4];
-        if (gi + 1u < 8u) {
-          tmem_ld8(tm_s + 8u * (gi + 1u), sb);
-          tmem_ld8(tm_d + 8u * (gi + 1u), db8);
-        }
-        const uint32_t chunk_off = (2u * wg + c) * static_cast<uint32_t>(kTableTileBytes) + tab_row + ((gq ^ tab_sw) << 4);
-        quad_group<T>(p.has_bias, p.has_mask, sa, da, smem_base + p.off_bias + chunk_off,
-                      smem_base + p.off_mask + mk.stage * kQTableBytes + chunk_off, lse2 + 8u * gi,
-                      delta + 8u * gi, scale, pw, dw);
-        // P^T and dS^T go back over the first 16 columns of this chunk's own S^T / dP^T columns
-        tmem_st4(tm_s + 32u * c + 4u * gq, pw);
-        tmem_st4(tm_d + 32u * c + 4u * gq, dw);
-        tmem_wait_ld();   // the next group's registers may be read from here on
+      for (uint32_t c = 0; c < 2u; ++c) {
+        uint32_t wsel[16];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          sa[i] = sb[i];
-          da[i] = db8[i];
+        for (int i = 0; i < 16; ++i) wsel[i] = c == 0u ? wb[i] : wb[16 + i];
+        const uint32_t mchunk = mask_row + (2u * wg + c) * static_cast<uint32_t>(kTableTileBytes);
+#pragma unroll
+        for (uint32_t hh = 0; hh < 2u; ++hh) {
+          uint32_t sv[16], dv[16], pw[8], dw[8];
+          tmem_ld16(tm_s + 32u * c + 16u * hh, sv);
+          tmem_ld16(tm_d + 32u * c + 16u * hh, dv);
+          tmem_wait_ld();
+          quad_half<T>(sv, dv, &wsel[8 * hh], p.has_mask != 0, mchunk + (((2u * hh) ^ tab_sw) << 4),
+                       mchunk + (((2u * hh + 1u) ^ tab_sw) << 4), nl2 + 32u * c + 16u * hh, nd + 32u * c + 16u * hh,
+                       scale, pw, dw);
+          // P^T and dS^T go back over the first 16 columns of this chunk's own S^T / dP^T
+          // columns (columns whose scores were read in an earlier piece or in this one)
+          tmem_st8(tm_s + 32u * c + 8u * hh, pw);
+          tmem_st8(tm_d + 32u * c + 8u * hh, dw);
         }
       }
     }
+    QPROF_SEG(10);
     if (p.has_mask) {
       mbar_arrive(bar(qbMaskFree + mk.stage));
       mk.advance();
     }
     tmem_wait_st();
+    QPROF_SEG(11);
     // dS also goes to shared memory (A operand of dQ^ += dS K^), but only now: the product that
     // read the previous job's copy was issued while this step was being computed, so it is
     // normally done and this wait costs nothing.  The packed words are read back from tensor
-    // memory (the loop above is rolled and cannot keep them in registers).
+    // memory rather than kept in 32 more registers.
     if (n > 0) {
-      if (!mbar_wait(bar(qbDsFree), par ^ 1u, ctx, 53)) return;
+      if (!qwait(bar(qbDsFree), par ^ 1u, ctx, 53)) return;
     }
 #pragma unroll
     for (uint32_t c = 0; c < 2u; ++c) {
@@ -216,6 +286,7 @@ __device__ void quad_compute_role(const QuadParams& p, uint8_t* smem_ptr, uint32
     tc_fence_before();
     fence_proxy_async_smem();
     mbar_arrive(bar(qbPReady + wg));
+    QPROF_SEG(12);
     st.advance();
   }
 
@@ -223,7 +294,7 @@ __device__ void quad_compute_role(const QuadParams& p, uint8_t* smem_ptr, uint32
   // fed them (it precedes the last dQ product, whose completion the last barrier phase signals).
   // Warpgroup w writes the 64 query columns of its step; the partial buffer is laid out
   // (query, key) like the result.
-  if (!mbar_wait(bar(qbDsFree), (static_cast<uint32_t>(g.count) & 1u) ^ 1u, ctx, 56)) return;
+  if (!qwait(bar(qbDsFree), (static_cast<uint32_t>(g.count) & 1u) ^ 1u, ctx, 56)) return;
   if (p.db_partial != nullptr) {
     tc_fence_after();
     const int key = static_cast<int>(g.a * kTileRows + lt);
@@ -260,23 +331,42 @@ __device__ void quad_prepare_role(const QuadParams& p, uint8_t* smem_ptr, uint32
   float* rowstats = reinterpret_cast<float*>(smem_ptr + p.off_rowstats);
   const int ig = static_cast<int>(g.b * kTileRows + lt);
   const bool row_ok = ig < p.N;
+  // The O row and lse of a job come straight from global memory (first touch: a trip to DRAM).
+  // They are prefetched into L2 one job ahead (no registers held), so that the loads proper, issued
+  // before the wait for the job's tiles, are short.
+  auto row_ptr = [&](int n) {
+    const int bw = g.slot + n * p.nslots;
+    return static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
+  };
+  auto lse_ptr = [&](int n) {
+    const int bw = g.slot + n * p.nslots;
+    return p.lse + bw * p.lse_sbw + g.h * p.lse_sh + ig;
+  };
+  auto prefetch = [&](int n) {
+    if (row_ok && n < g.count) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(row_ptr(n)));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(lse_ptr(n)));
+    }
+  };
   Ring st(p.n_stages);
+  prefetch(0);
+  prefetch(1);
 #pragma unroll 1
   for (int n = 0; n < g.count; ++n) {
-    const int bw = g.slot + n * p.nslots;
+    prefetch(n + 2);
     uint4 o_row[4];
     float lse = 0.f;
     if (row_ok) {
-      const uint16_t* orow = static_cast<const uint16_t*>(p.o) + bw * p.o_sbw + g.h * p.o_sh + ig * p.o_sn;
+      const uint16_t* orow = row_ptr(n);
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) o_row[ch] = quad_ldg_v4(orow + ch * 8);
-      lse = __ldg(p.lse + bw * p.lse_sbw + g.h * p.lse_sh + ig);
+      lse = __ldg(lse_ptr(n));
     }
     const uint32_t base = smem_base + p.off_stage + st.stage * kQStageBytes;
-    if (!mbar_wait<true>(bars + 8u * (qbFull + st.stage), st.phase, ctx, 80)) return;
+    if (!qwait(bars + 8u * (qbFull + st.stage), st.phase, ctx, 80)) return;
     normalise_row<T>(base, lt);              // K^
     normalise_row<T>(base + 16384u, lt);     // Q^
-    float l2 = INFINITY, dl = 0.f;
+    float l2 = INFINITY, dl = 0.f;   // a row past the end of the window: p = exp2(-inf) = 0
     if (row_ok) {
       float dlp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -293,8 +383,8 @@ __device__ void quad_prepare_role(const QuadParams& p, uint8_t* smem_ptr, uint32
       dl = (dlp[0] + dlp[1]) + (dlp[2] + dlp[3]);
       l2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
     }
-    rowstats[st.stage * 256u + lt] = l2;
-    rowstats[st.stage * 256u + 128u + lt] = dl;
+    rowstats[st.stage * 256u + lt] = -l2;            // the compute warpgroups add, never subtract
+    rowstats[st.stage * 256u + 128u + lt] = -dl;
     fence_proxy_async_smem();
     mbar_arrive(bars + 8u * (qbReady + st.stage));
     st.advance();
@@ -334,49 +424,77 @@ __device__ void quad_epilogue_role(const QuadParams& p, uint8_t* smem_ptr, uint3
   for (int n = 0; n < g.count; ++n) {
     const int bw = g.slot + n * p.nslots;
     const uint32_t par = static_cast<uint32_t>(n) & 1u;
-    // the raw k / q rows for the Jacobians of this job's epilogue: requested first, used last
-    uint4 rawk[4], rawq[4];
+    // the raw k or q row for the Jacobian of this job's epilogue: requested first, used last
+    // (inside a cluster a thread finishes either dV and dK or dQ, so it needs one of the two)
+    uint4 raw[4];
 #pragma unroll
-    for (int ch = 0; ch < 4; ++ch) rawk[ch] = rawq[ch] = make_uint4(0u, 0u, 0u, 0u);
-    if (keeper && k_ok) {
-      const uint16_t* src = static_cast<const uint16_t*>(p.k) + bw * p.k_sbw + g.h * p.k_sh + krow * p.k_sn;
+    for (int ch = 0; ch < 4; ++ch) raw[ch] = make_uint4(0u, 0u, 0u, 0u);
+    const uint16_t* qsrc = static_cast<const uint16_t*>(p.q) + bw * p.q_sbw + g.h * p.q_sh + qrow * p.q_sn;
+    if (keeper) {
+      if (k_ok) {
+        const uint16_t* src = static_cast<const uint16_t*>(p.k) + bw * p.k_sbw + g.h * p.k_sh + krow * p.k_sn;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) rawk[ch] = quad_ldg_v4(src + ch * 8);
+        for (int ch = 0; ch < 4; ++ch) raw[ch] = quad_ldg_v4(src + ch * 8);
+      }
+    } else if (q_ok) {
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) raw[ch] = quad_ldg_v4(qsrc + ch * 8);
     }
-    if (fin_q && q_ok) {
-      const uint16_t* src = static_cast<const uint16_t*>(p.q) + bw * p.q_sbw + g.h * p.q_sh + qrow * p.q_sn;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) rawq[ch] = quad_ldg_v4(src + ch * 8);
+    // what the partners will push for this job: 64 rows x 128 bytes per accumulator I finish
+    if (quad && row64 == 0u) {
+      if (keeper) {
+        mbar_arrive_expect_tx(bar(qbRecvFull + 0), kQRecvPart);
+        mbar_arrive_expect_tx(bar(qbRecvFull + 1), kQRecvPart);
+      } else {
+        mbar_arrive_expect_tx(bar(qbRecvFull + 2), kQRecvPart);
+      }
     }
-    // all three accumulators go to registers at once, so that the tensor core can start the next
-    // job's sums while the exchange and the epilogues run
-    if (!mbar_wait(bar(qbAccFull), par, ctx, 55)) return;
+    if (!qwait(bar(qbAccFull), par, ctx, 55)) return;
     tc_fence_after();
-    uint32_t rv[32], rk[32], rq[32];
-    tmem_ld32(tmem + lane_base + kQTmDV, rv);
-    tmem_ld32(tmem + lane_base + kQTmDK, rk);
-    tmem_ld32(tmem + lane_base + kQTmDQ, rq);
-    tmem_wait_ld();
-    tc_fence_before();
-    mbar_arrive(bar(qbAccFree));
-
-    // X: 0 dV, 1 dK, 2 dQ
-    auto push = [&](const uint32_t (&r)[32], uint32_t X) -> bool {
-      const uint32_t partner = rank ^ (X == 2u ? 2u : 1u);
-      // the partner has read what I pushed for the previous job
-      if (!mbar_wait_cluster(bar(qbRecvFree + X), par ^ 1u, ctx, 58)) return false;
-      const uint32_t dst = cluster_map(recv_base + X * kQRecvPart + row64 * 128u, partner);
+    QPROF_BEGIN();
+    // One trip per accumulator (0 dV, 1 dK, 2 dQ), rolled, so that the pushing and the finishing
+    // code exist once (the kernel's roles have to fit the instruction cache together).  dV and dK
+    // are read in the same trip: the tensor core needs both back at the start of the next job (dQ
+    // only at its end).  A keeper pushes dQ and finishes dV and dK; the others push dV and dK and
+    // finish dQ; without a cluster every thread finishes all three.  Every thread pushes before it
+    // finishes, so the pushes a finishing thread waits for never wait for that thread.
+    uint32_t hold[32];
+#pragma unroll 1
+    for (uint32_t t = 0; t < 3u; ++t) {
+      // a keeper starts with its push (dQ), then dV, dK; everybody else goes 0, 1, 2
+      const uint32_t X = (quad && keeper) ? (t == 0u ? 2u : t - 1u) : t;
+      uint32_t r[32];
+      if (X == 0u) {
+        tmem_ld32(tmem + lane_base + kQTmDV, r);
+        tmem_ld32(tmem + lane_base + kQTmDK, hold);
+      } else if (X == 2u) {
+        tmem_ld32(tmem + lane_base + kQTmDQ, r);
+      }
+      tmem_wait_ld();
+      QPROF_SEG(0);
+      if (X != 1u) {
+        tc_fence_before();
+        mbar_arrive(bar(X == 0u ? qbAccFree : qbAccFreeQ));
+      } else {
 #pragma unroll
-      for (uint32_t ch = 0; ch < 8u; ++ch) st_cluster_v4(dst + ((ch ^ row_sw) << 4), &r[4 * ch]);
-      mbar_arrive_cluster(cluster_map(bar(qbRecvFull + X), partner));
-      return true;
-    };
-    // rows of dV are stored as they are; rows of dK^ / dQ^ go through the Jacobian of the
-    // L2 normalisation: dx = scale (dX' - x^ (x^ . dX')) / |x| from the raw row x
-    auto finish = [&](uint32_t (&r)[32], uint32_t X, const uint4 (&raw)[4], bool ok, uint16_t* dst) -> bool {
+        for (int i = 0; i < 32; ++i) r[i] = hold[i];
+      }
+      const uint32_t partner = rank ^ (X == 2u ? 2u : 1u);
+      const bool push = quad && (keeper ? X == 2u : X != 2u);
+      if (push) {
+        // the partner has read what I pushed for the previous job; each 16-byte piece credits
+        // the partner's barrier when it has landed there
+        if (!qwait<true>(bar(qbRecvFree + X), par ^ 1u, ctx, 58)) return;
+        const uint32_t dst = cluster_map(recv_base + X * kQRecvPart + row64 * 128u, partner);
+        const uint32_t full = cluster_map(bar(qbRecvFull + X), partner);
+#pragma unroll
+        for (uint32_t ch = 0; ch < 8u; ++ch) st_async_cluster_v4(dst + ((ch ^ row_sw) << 4), &r[4 * ch], full);
+        QPROF_SEG(1);
+        continue;
+      }
       if (quad) {
-        const uint32_t partner = rank ^ (X == 2u ? 2u : 1u);
-        if (!mbar_wait_cluster(bar(qbRecvFull + X), par, ctx, 59)) return false;
+        if (!qwait<true>(bar(qbRecvFull + X), par, ctx, 59)) return;
+        QPROF_SEG(2);
         const uint32_t src = recv_base + X * kQRecvPart + row64 * 128u;
 #pragma unroll
         for (uint32_t ch = 0; ch < 8u; ++ch) {
@@ -386,8 +504,18 @@ __device__ void quad_epilogue_role(const QuadParams& p, uint8_t* smem_ptr, uint3
           for (int i = 0; i < 4; ++i)
             r[4 * ch + i] = __float_as_uint(__uint_as_float(r[4 * ch + i]) + __uint_as_float(w4[i]));
         }
-        mbar_arrive_cluster(cluster_map(bar(qbRecvFree + X), partner));
+        // (the additions above have consumed every loaded value: the buffer may be overwritten)
+        mbar_arrive_cluster_relaxed(cluster_map(bar(qbRecvFree + X), partner));
+        QPROF_SEG(3);
       }
+      const bool ok = X == 2u ? q_ok : k_ok;
+      if (X == 2u && keeper) {
+        // without a cluster this thread finishes all three: the q row is fetched only now
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) raw[ch] = q_ok ? quad_ldg_v4(qsrc + ch * 8) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      // rows of dV are stored as they are; rows of dK^ / dQ^ go through the Jacobian of the
+      // L2 normalisation: dx = scale (dX' - x^ (x^ . dX')) / |x| from the raw row x
       float fmul = 1.f, cq = 0.f;
       if (X != 0u) {
         float ss = 0.f, qd = 0.f;
@@ -409,7 +537,12 @@ __device__ void quad_epilogue_role(const QuadParams& p, uint8_t* smem_ptr, uint3
         fmul = scale * rn;
         cq = rn * dot;
       }
+      QPROF_SEG(4);
       if (ok) {
+        uint16_t* dst;
+        if (X == 0u) dst = static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + krow * p.dv_sn;
+        else if (X == 1u) dst = static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + krow * p.dk_sn;
+        else dst = static_cast<uint16_t*>(p.dq) + bw * p.dq_sbw + g.h * p.dq_sh + qrow * p.dq_sn;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           const uint32_t w4[4] = {raw[ch].x, raw[ch].y, raw[ch].z, raw[ch].w};
@@ -426,34 +559,28 @@ __device__ void quad_epilogue_role(const QuadParams& p, uint8_t* smem_ptr, uint3
           *reinterpret_cast<uint4*>(dst + 8 * ch) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
         }
       }
-      return true;
-    };
-    // pushes first, so that no push ever waits behind a thread that waits for a push
-    if (quad) {
-      if (keeper) {
-        if (!push(rq, 2u)) return;
-      } else {
-        if (!push(rv, 0u)) return;
-        if (!push(rk, 1u)) return;
-      }
-    }
-    if (keeper) {
-      // (dV has no Jacobian: the raw row passed for it is not used)
-      if (!finish(rv, 0u, rawq, k_ok,
-                  static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + krow * p.dv_sn)) return;
-      if (!finish(rk, 1u, rawk, k_ok,
-                  static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + krow * p.dk_sn)) return;
-    }
-    if (fin_q) {
-      if (!finish(rq, 2u, rawq, q_ok,
-                  static_cast<uint16_t*>(p.dq) + bw * p.dq_sbw + g.h * p.dq_sh + qrow * p.dq_sn)) return;
+      QPROF_SEG(5);
     }
   }
 }
 
-// ------------------------------------------------------------------------------------------------
-// MMA issuer (one thread)
-// ------------------------------------------------------------------------------------------------
+// The issuing thread is the busiest in the CTA (some forty products per job), so a job is written
+// out as straight-line code: tensor-memory addresses and descriptor offsets are constants, and a
+// descriptor costs one addition (the stage's base address, in 16-byte units, plus a constant).
+struct Desc16 {
+  uint32_t lo, hi;   // descriptor for shared-memory address 0; add (address >> 4) to lo
+};
+__device__ __forceinline__ Desc16 make_desc16(uint32_t lbo_bytes, uint32_t sbo_bytes, SmemSwizzle sw) {
+  const DescBase b = make_desc_base(0, lbo_bytes, sbo_bytes, sw);
+  return Desc16{b.lo, b.hi};
+}
+__device__ __forceinline__ uint64_t desc16_at(const Desc16& d, uint32_t base16, uint32_t const_bytes) {
+  return (static_cast<uint64_t>(d.hi) << 32) | static_cast<uint64_t>(d.lo + base16 + (const_bytes >> 4));
+}
+// (inside a cluster the shared-memory address of a CTA other than rank 0 carries the rank above
+// bit 24: only the offset inside the CTA's own window belongs in a descriptor)
+__device__ __forceinline__ uint32_t smem16(uint32_t addr) { return (addr & 0x3FFFFu) >> 4; }
+
 template <typename T>
 __device__ void quad_mma_role(const QuadParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
                               const WaitCtx& ctx, uint32_t rank) {
@@ -461,84 +588,118 @@ __device__ void quad_mma_role(const QuadParams& p, uint32_t smem_base, uint32_t 
   if (g.count == 0) return;
   constexpr uint32_t fmt = Elem<T>::kFmt;
   auto bar = [&](int i) { return bars + 8u * i; };
-  const uint32_t idesc_s = make_idesc(fmt, 128, kStepCols, 0, 0);
-  const uint32_t idesc_acc = make_idesc(fmt, 128, 32, 0, 1);   // A in TMEM, B MN-major
-  const uint32_t idesc_dq = make_idesc(fmt, 128, 32, 1, 1);    // A and B MN-major
-  const DescBase dk64 = make_desc_base(0, 16, 512, kSw64);      // K-major rows of 64 bytes
-  const DescBase dm64 = make_desc_base(0, 512, 512, kSw64);     // MN-major rows of 64 bytes
-  const DescBase dds = make_desc_base(0, 16384, 1024, kSw128);  // dS tile, MN-major, two slabs
+  constexpr uint32_t idesc_s = make_idesc(fmt, 128, kStepCols, 0, 0);
+  constexpr uint32_t idesc_acc = make_idesc(fmt, 128, 32, 0, 1);   // A in TMEM, B MN-major
+  constexpr uint32_t idesc_dq = make_idesc(fmt, 128, 32, 1, 1);    // A and B MN-major
+  const Desc16 dk64 = make_desc16(16, 512, kSw64);      // K-major rows of 64 bytes
+  const Desc16 dm64 = make_desc16(512, 512, kSw64);     // MN-major rows of 64 bytes
+  const Desc16 dds = make_desc16(16384, 1024, kSw128);  // dS tile, MN-major, two slabs
   const bool with_db = p.db_partial != nullptr;
-  const uint32_t ident = smem_base + p.off_ident;
-  const uint32_t ds_base = smem_base + p.off_ds;
+  const uint32_t ident16_c = smem16(smem_base + p.off_ident);
+  const uint32_t ds16_c = smem16(smem_base + p.off_ds);
+  // Per-job copies that the compiler must treat as fresh values: otherwise it computes the some
+  // forty (base + constant) addresses of a job once, outside the loop, and keeps them all in
+  // registers that this thread does not have.
+  uint32_t tm = tmem, ident16 = ident16_c, ds16 = ds16_c;
+  auto refresh = [&]() {
+    tm = tmem;
+    ident16 = ident16_c;
+    ds16 = ds16_c;
+    asm volatile("" : "+r"(tm), "+r"(ident16), "+r"(ds16));
+  };
+  constexpr uint32_t kK = 0u, kV = 8192u, kQ = 16384u, kDO = 24576u;   // byte offsets inside a stage
 
-  // S^T = K^ Q^^T and dP^T = V dO^T for the 64 queries of step w
-  auto issue_sdp = [&](uint32_t w, uint32_t stage_base) {
-    const uint32_t row_off = w * (kStepCols * kRowBytes);
-    const uint32_t st_ = tmem + w * 128u + kQTmS, dpt = tmem + w * 128u + kQTmDP;
+  // S^T = K^ Q^^T and dP^T = V dO^T for the 64 queries of step W (a compile-time constant)
+  auto issue_sdp = [&](auto W, uint32_t s16) {
+    constexpr uint32_t w = decltype(W)::value;
+    constexpr uint32_t row_off = w * (kStepCols * kRowBytes);
 #pragma unroll
     for (uint32_t k = 0; k < 2u; ++k) {
-      mma_ss(st_, desc_at(dk64, stage_base + 32u * k), desc_at(dk64, stage_base + 16384u + row_off + 32u * k),
+      mma_ss(tm + w * 128u + kQTmS, desc16_at(dk64, s16, kK + 32u * k), desc16_at(dk64, s16, kQ + row_off + 32u * k),
              idesc_s, k);
-      mma_ss(dpt, desc_at(dk64, stage_base + 8192u + 32u * k),
-             desc_at(dk64, stage_base + 24576u + row_off + 32u * k), idesc_s, k);
+      mma_ss(tm + w * 128u + kQTmDP, desc16_at(dk64, s16, kV + 32u * k),
+             desc16_at(dk64, s16, kDO + row_off + 32u * k), idesc_s, k);
     }
     mma_commit(bar(qbSFull + static_cast<int>(w)));
   };
+  // dV += P^T dO, dK^ += dS^T Q^, dB^T += dS^T I for step W (each step has its own copy of the
+  // identity tile)
+  auto issue_acc = [&](auto W, uint32_t s16) {
+    constexpr uint32_t w = decltype(W)::value;
+#pragma unroll
+    for (uint32_t c = 0; c < 2u; ++c) {
+#pragma unroll
+      for (uint32_t k = 0; k < 2u; ++k) {
+        const uint32_t row_off = (w * kStepCols + c * kChunkCols) * kRowBytes + k * 1024u;
+        const uint32_t a_p = tm + w * 128u + kQTmS + 32u * c + 8u * k;
+        const uint32_t a_ds = tm + w * 128u + kQTmDP + 32u * c + 8u * k;
+        const uint32_t acc = (w | c | k) ? 1u : 0u;
+        mma_ts(tm + kQTmDV, a_p, desc16_at(dm64, s16, kDO + row_off), idesc_acc, acc);
+        mma_ts(tm + kQTmDK, a_ds, desc16_at(dm64, s16, kQ + row_off), idesc_acc, acc);
+        if (with_db)
+          mma_ts(tm + kQTmDB + 64u * w + 32u * c, a_ds, desc16_at(dm64, ident16, 2048u * w + k * 1024u), idesc_acc, 1u);
+      }
+    }
+  };
+  using W0 = std::integral_constant<uint32_t, 0u>;
+  using W1 = std::integral_constant<uint32_t, 1u>;
 
   Ring st(p.n_stages);
-  if (!mbar_wait(bar(qbReady + 0), 0u, ctx, 60)) return;
+  if (!qwait(bar(qbReady + 0), 0u, ctx, 60)) return;
   tc_fence_after();
+  {
+    // the first job's scores (runs once: a small rolled loop instead of two more copies)
+    const uint32_t s16 = smem16(smem_base + p.off_stage);
 #pragma unroll 1
-  for (uint32_t w = 0; w < 2u; ++w) issue_sdp(w, smem_base + p.off_stage);
+    for (uint32_t w = 0; w < 2u; ++w) {
+      const uint32_t row_off = w * (kStepCols * kRowBytes);
+#pragma unroll 1
+      for (uint32_t k = 0; k < 2u; ++k) {
+        mma_ss(tmem + w * 128u + kQTmS, desc16_at(dk64, s16, kK + 32u * k), desc16_at(dk64, s16, kQ + row_off + 32u * k),
+               idesc_s, k);
+        mma_ss(tmem + w * 128u + kQTmDP, desc16_at(dk64, s16, kV + 32u * k),
+               desc16_at(dk64, s16, kDO + row_off + 32u * k), idesc_s, k);
+      }
+      mma_commit(bar(qbSFull + static_cast<int>(w)));
+    }
+  }
 
 #pragma unroll 1
   for (int n = 0; n < g.count; ++n) {
     const uint32_t par = static_cast<uint32_t>(n) & 1u;
-    const uint32_t base = smem_base + p.off_stage + st.stage * kQStageBytes;
+    refresh();
+    const uint32_t s16 = smem16(smem_base + p.off_stage + st.stage * kQStageBytes);
     const bool has_next = n + 1 < g.count;
     Ring nx = st;
     nx.advance();
+    const uint32_t n16 = smem16(smem_base + p.off_stage + nx.stage * kQStageBytes);
     // the accumulators of the previous job have been read out
     if (n > 0) {
-      if (!mbar_wait(bar(qbAccFree), par ^ 1u, ctx, 62)) return;
+      if (!qwait(bar(qbAccFree), par ^ 1u, ctx, 62)) return;
     }
-#pragma unroll 1
-    for (uint32_t w = 0; w < 2u; ++w) {
-      if (!mbar_wait(bar(qbPReady + static_cast<int>(w)), par, ctx, 64)) return;
+    if (!qwait(bar(qbPReady + 0), par, ctx, 64)) return;
+    tc_fence_after();
+    issue_acc(W0{}, s16);
+    // the next job's scores of step 0 go over this job's P^T / dS^T of the step (the tensor core
+    // works in issue order), so that warpgroup 0 can go on while the rest is issued
+    if (has_next) {
+      if (!qwait(bar(qbReady + nx.stage), nx.phase, ctx, 66)) return;
       tc_fence_after();
-#pragma unroll 1
-      for (uint32_t c = 0; c < 2u; ++c) {
-        const uint32_t row_off = (w * kStepCols + c * kChunkCols) * kRowBytes;
-        const uint32_t a_p = tmem + w * 128u + kQTmS + 32u * c, a_ds = tmem + w * 128u + kQTmDP + 32u * c;
-#pragma unroll
-        for (uint32_t k = 0; k < 2u; ++k) {
-          const uint32_t acc = (w | c | k) ? 1u : 0u;
-          mma_ts(tmem + kQTmDV, a_p + k * 8u, desc_at(dm64, base + 24576u + row_off + k * 1024u), idesc_acc, acc);
-          mma_ts(tmem + kQTmDK, a_ds + k * 8u, desc_at(dm64, base + 16384u + row_off + k * 1024u), idesc_acc, acc);
-          // dB^T += dS^T I: the tensor core sums over the windows of this cluster (each step has
-          // its own copy of the identity tile)
-          if (with_db)
-            mma_ts(tmem + kQTmDB + 64u * w + 32u * c, a_ds + k * 8u, desc_at(dm64, ident + 2048u * w + k * 1024u),
-                   idesc_acc, 1u);
-        }
-      }
-      // the next job's scores of step w go over this job's P^T / dS^T of the step (the tensor
-      // core works in issue order), so that warpgroup w can go on while the rest is issued
-      if (has_next) {
-        if (w == 0u) {
-          if (!mbar_wait(bar(qbReady + nx.stage), nx.phase, ctx, 66)) return;
-          tc_fence_after();
-        }
-        issue_sdp(w, smem_base + p.off_stage + nx.stage * kQStageBytes);
-      }
+      issue_sdp(W0{}, n16);
     }
-    // dQ^ = dS K^ over the 128 keys of the block
-#pragma unroll 2
+    if (!qwait(bar(qbPReady + 1), par, ctx, 65)) return;
+    tc_fence_after();
+    issue_acc(W1{}, s16);
+    if (has_next) issue_sdp(W1{}, n16);
+    // dQ^ = dS K^ over the 128 keys of the block (the previous job's dQ has been read out)
+    if (n > 0) {
+      if (!qwait(bar(qbAccFreeQ), par ^ 1u, ctx, 63)) return;
+    }
+#pragma unroll
     for (uint32_t k = 0; k < 8u; ++k)
-      mma_ss(tmem + kQTmDQ, desc_at(dds, ds_base + k * 2048u), desc_at(dm64, base + k * 1024u), idesc_dq, k);
+      mma_ss(tm + kQTmDQ, desc16_at(dds, ds16, k * 2048u), desc16_at(dm64, s16, kK + k * 1024u), idesc_dq, k);
     mma_commit(bar(qbAccFull));
     mma_commit(bar(qbDsFree));
-    // (the next job's scores, issued above, read only the next stage)
     mma_commit(bar(qbFree + st.stage));
     st = nx;
   }
@@ -563,12 +724,11 @@ __device__ void quad_load_role(const QuadParams& p, uint32_t smem_base, uint32_t
                     k0 + hb * kBoxRows, plane);
     }
   };
-  if (p.has_bias) load_table(smem_base + p.off_bias, &p.tm_biasT, bar(qbBiasFull), g.h);
   Ring st(p.n_stages), mk(p.n_mask_stages);
 #pragma unroll 1
   for (int n = 0; n < g.count; ++n) {
     const int bw = g.slot + n * p.nslots;
-    if (!mbar_wait<true>(bar(qbFree + st.stage), st.phase ^ 1u, ctx, 70)) return;
+    if (!qwait(bar(qbFree + st.stage), st.phase ^ 1u, ctx, 70)) return;
     const uint32_t base = smem_base + p.off_stage + st.stage * kQStageBytes;
     const uint32_t full = bar(qbFull + st.stage);
     mbar_arrive_expect_tx(full, kQStageBytes);
@@ -581,7 +741,7 @@ __device__ void quad_load_role(const QuadParams& p, uint32_t smem_base, uint32_t
     }
     st.advance();
     if (p.has_mask) {
-      if (!mbar_wait<true>(bar(qbMaskFree + mk.stage), mk.phase ^ 1u, ctx, 72)) return;
+      if (!qwait(bar(qbMaskFree + mk.stage), mk.phase ^ 1u, ctx, 72)) return;
       load_table(smem_base + p.off_mask + mk.stage * kQTableBytes, &p.tm_maskT, bar(qbMaskFull + mk.stage),
                  bw % p.nW);
       mk.advance();
@@ -617,8 +777,9 @@ __global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_
       if (i >= qbReady && i < qbFree) count = 128u;            // the preparing warpgroup
       else if (i >= qbMaskFree && i < qbBiasFull) count = 256u;
       else if (i >= qbPReady && i < qbAccFull) count = 128u;
-      else if (i == qbAccFree) count = 128u;                   // the epilogue warpgroup
-      else if (i >= qbRecvFull && i < qbDsFree) count = 64u;
+      else if (i == qbAccFree || i == qbAccFreeQ) count = 128u; // the epilogue warpgroup
+      else if (i >= qbRecvFull && i < qbRecvFree) count = 1u;  // one arrive.expect_tx; the data credits the rest
+      else if (i >= qbRecvFree && i < qbDsFree) count = 64u;
       mbar_init(bars + 8u * i, count);
     }
     mbar_fence_init();
@@ -626,7 +787,6 @@ __global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_
     tma_prefetch_desc(&p.tm_k);
     tma_prefetch_desc(&p.tm_v);
     tma_prefetch_desc(&p.tm_do);
-    if (p.has_bias) tma_prefetch_desc(&p.tm_biasT);
     if (p.has_mask) tma_prefetch_desc(&p.tm_maskT);
   }
   if (warp == 16) {
@@ -655,13 +815,15 @@ __global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_
   WaitCtx ctx{&ctrl_words[1], p.status, p.prof};
 #if FWA2_TRACE
   const long long prof_t0 = clock64();
+  unsigned long long prof_g0 = 0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
 #endif
 
   float dscale_acc = 0.f;
   // 640 threads start with 96 registers each.  setmaxnreg only moves registers inside what the
   // CTA was given at launch (an increase beyond it would wait for ever), so the four budgets
   // below must not add up to more than 640 x 96.
-  constexpr uint32_t kRegCompute = 120, kRegEpilogue = 144, kRegPrepare = 48, kRegIssue = 48;
+  constexpr uint32_t kRegCompute = 128, kRegEpilogue = 128, kRegPrepare = 56, kRegIssue = 40;
   static_assert(2 * 128 * kRegCompute + 128 * (kRegEpilogue + kRegPrepare + kRegIssue) <= kQuadThreads * 96,
                 "register budgets exceed the launch allocation");
   if (warp < 8) {
@@ -701,6 +863,15 @@ __global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_
   if (tid == 0 && blockIdx.x == 0 && p.prof != nullptr) {
     p.prof[0] = static_cast<unsigned long long>(clock64() - prof_t0);
     p.prof[1] = static_cast<unsigned long long>(quad_geom(p, rank).count);
+  }
+  if (tid == 0 && p.prof != nullptr && blockIdx.x < 160) {
+    unsigned long long g1;
+    uint32_t smid;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    p.prof[256 + 3 * blockIdx.x] = prof_g0;
+    p.prof[257 + 3 * blockIdx.x] = g1;
+    p.prof[258 + 3 * blockIdx.x] = smid;
   }
 #endif
   if (tid == 0) report_abort(ctrl_words[1], p.status);

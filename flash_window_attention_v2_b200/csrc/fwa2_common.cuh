@@ -200,7 +200,9 @@ struct BwdParams {
 // so each CTA keeps its tile of the window-summed dBias in tensor memory for the whole kernel.
 struct QuadParams {
   CUtensorMap tm_q, tm_k, tm_v, tm_do;   // 4-D (d, N, H, BW), box (32, 64, 1, 1)
-  CUtensorMap tm_biasT, tm_maskT;        // 3-D transposed tables (N_pad, N, planes), box (32, 64, 1)
+  CUtensorMap tm_maskT;                  // 3-D transposed mask (N_pad, N, nW), box (32, 64, 1)
+  const void* bias_t;                    // transposed bias (H, key, table_pitch queries), 16 bit
+  int table_pitch;
   const void* q;  long long q_sbw, q_sh, q_sn;
   const void* k;  long long k_sbw, k_sh, k_sn;
   const void* o;  long long o_sbw, o_sh, o_sn;
@@ -222,11 +224,10 @@ struct QuadParams {
   int n_stages, n_mask_stages;
   uint32_t off_stage;         // n_stages x [K | V | Q | dO], 8 KiB each
   uint32_t off_mask;          // n_mask_stages x four chunks of (128 keys x 32 queries) mask^T
-  uint32_t off_bias;          // the same four chunks of bias^T, loaded once
   uint32_t off_ds;            // dS tile, 32 KiB (two slabs of 64 queries)
   uint32_t off_recv;          // three partial accumulators of 64 rows x 32 fp32 pushed by peers
   uint32_t off_ident;         // two 32 x 32 identity tiles
-  uint32_t off_rowstats;      // n_stages x (128 lse*log2e, 128 delta) floats
+  uint32_t off_rowstats;      // n_stages x (128 x -lse*log2e, 128 x -delta) floats
   uint32_t off_ctrl;
   uint32_t smem_bytes;
   DeviceStatus* status;

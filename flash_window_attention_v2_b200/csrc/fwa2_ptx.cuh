@@ -195,6 +195,23 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
 }
+// An arrival that orders nothing: for "I have finished READING your buffer" signals, issued after
+// the instructions that consumed the loaded values (a release at cluster scope would also wait
+// for every global store the thread still has in flight).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// 16 bytes into a peer's shared memory; the peer's mbarrier (in the same CTA as the destination)
+// is credited with 16 transaction bytes when the data has landed, so the sender needs no fence
+// and no arrival of its own.
+__device__ __forceinline__ void st_async_cluster_v4(uint32_t cluster_addr, const uint32_t* v,
+                                                    uint32_t cluster_mbar) {
+  asm volatile(
+      "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+      ::"r"(cluster_addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(cluster_mbar)
+      : "memory");
+}
 __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

@@ -14,6 +14,7 @@ from typing import List, Optional
 
 import torch
 
+from . import kernels as _kernels
 from .flash_window_attention_v2 import flash_win_attn_v2_func
 
 
@@ -51,5 +52,7 @@ class GraphedStep:
             self.outputs: List[torch.Tensor] = step()
 
     def replay(self) -> List[torch.Tensor]:
+        # a device-side timeout of an earlier replay shows up here (host read of a pinned word)
+        _kernels.poll_device_status(self.q.device)
         self.graph.replay()
         return self.outputs

@@ -103,3 +103,6 @@ class HostBatchPipeline:
         self.s_in.synchronize()
         torch.cuda.current_stream(self.device).synchronize()
         self.s_out.synchronize()
+        # everything has finished: a device-side timeout of any submitted batch is visible now
+        from . import kernels
+        kernels.poll_device_status(self.device)

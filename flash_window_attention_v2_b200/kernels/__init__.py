@@ -20,31 +20,76 @@ import torch
 
 from .. import _lib
 
-__all__ = ["_flash_attn_forward", "_flash_attn_backward", "check_device_status", "finalize_grads"]
+__all__ = ["_flash_attn_forward", "_flash_attn_backward", "check_device_status", "poll_device_status",
+           "DeviceTimeoutError", "finalize_grads"]
 
 _DTYPES = {torch.float16: _lib.FWA2_F16, torch.bfloat16: _lib.FWA2_BF16}
-_status_words: dict[int, torch.Tensor] = {}
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+# Per device: (status block in device memory, its mirror in pinned host memory).  A kernel whose
+# bounded wait ran out writes the device block; every backward call ends with an asynchronous
+# 16-byte copy into the mirror, and every boundary call starts by looking at the mirror, so a
+# device-side timeout surfaces as an exception one or two calls later without any host
+# synchronisation on the normal path.
+_status_words: dict[int, tuple] = {}
+
+
+class DeviceTimeoutError(RuntimeError):
+    """A bounded wait inside a kernel ran out; the outputs of that call are incomplete."""
+
+
+def _status_entry(device: torch.device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ent = _status_words.get(idx)
+    if ent is None:
+        dev_block = torch.zeros(4, dtype=torch.int32, device=device)
+        host_block = torch.zeros(4, dtype=torch.int32).pin_memory()
+        ent = (dev_block, host_block)
+        _status_words[idx] = ent
+    return ent
 
 
 def _status(device: torch.device) -> torch.Tensor:
+    return _status_entry(device)[0]
+
+
+def _describe(st) -> str:
+    return (f"fwa2 device status: a bounded wait ran out at site {st[0] >> 8} (kind {st[0] & 255}), "
+            f"block {st[1]}, detail {st[2]}; outputs of the affected call are incomplete")
+
+
+def poll_device_status(device=None) -> None:
+    """Raise if an earlier call on `device` reported a device-side timeout.  Reads the pinned host
+    mirror only: no synchronisation, safe to call anywhere (also while a stream is capturing)."""
+    if not _status_words:
+        return
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    t = _status_words.get(idx)
-    if t is None:
-        t = torch.zeros(4, dtype=torch.int32, device=device)
-        _status_words[idx] = t
-    return t
+    ent = _status_words.get(idx)
+    if ent is None:
+        return
+    st = ent[1].tolist()
+    if st[0] != 0:
+        ent[1].zero_()
+        if ent[0].is_cuda and not torch.cuda.is_current_stream_capturing():
+            ent[0].zero_()     # (while capturing, the block is cleared by the next synchronous check)
+        raise DeviceTimeoutError(_describe(st))
+
+
+def _mirror_status(device: torch.device) -> None:
+    """Enqueue the 16-byte copy of the status block into its pinned mirror on the current stream."""
+    dev_block, host_block = _status_entry(device)
+    host_block.copy_(dev_block, non_blocking=True)
 
 
 def check_device_status(device=None) -> None:
     """Synchronise and raise if a kernel recorded a device-side timeout."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     torch.cuda.synchronize(device)
-    st = _status(device).cpu().tolist()
+    dev_block, host_block = _status_entry(device)
+    st = dev_block.cpu().tolist()
     if st[0] != 0:
-        _status(device).zero_()
-        raise RuntimeError(f"fwa2 device status: site {st[0] >> 8}, kind {st[0] & 255}, "
-                           f"block {st[1]}, detail {st[2]}")
+        dev_block.zero_()
+        host_block.zero_()
+        raise DeviceTimeoutError(_describe(st))
 
 
 def _t4(x: torch.Tensor) -> _lib.Tensor4:
@@ -80,6 +125,7 @@ def _stream(device) -> C.c_void_p:
 
 def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="scalar",
                         _variant: int = 0, _max_ctas: int = 0, _trace=None):
+    poll_device_status(q.device)      # a timeout reported by an earlier call must not stay silent
     batch_window_size, n_heads, seqlen_q, d = q.shape
     _, _, seqlen_k, _ = k.shape
     assert k.shape == (batch_window_size, n_heads, seqlen_k, d)
@@ -153,6 +199,7 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
     multi-GPU path: when given, the window-summed dBias / dLogitScale are left there in fp32
     (before the clamp gate and the cast) and `db` / `dscale` are not written.
     """
+    poll_device_status(q.device)
     if do.stride(-1) != 1:
         do = do.contiguous()
     batch_window_size, n_heads, seqlen_q, d = q.shape
@@ -229,6 +276,7 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
             a.trace = _trace.data_ptr()
             a.trace_entries = _trace.numel() // 4
         _lib.check(L.fwa2_backward(C.byref(a), _stream(q.device)), "fwa2_backward")
+        _mirror_status(q.device)
 
     for dst, src in zip((dq, dk, dv), outs):
         if dst is not src:

@@ -158,6 +158,8 @@ class GraphedShardedStep:
             self.o, self.dq, self.dk, self.dv, self.partial = local()
 
     def replay(self):
+        from . import kernels
+        kernels.poll_device_status(self.q.device)
         self.graph.replay()
         db = dscale = None
         if self.partial is not None:
