@@ -20,6 +20,7 @@ cudaError_t launch_transpose_tables(const void* bias, long long bias_pitch, void
                                     const void* mask, long long mask_pitch, void* mask_t, int n_bias,
                                     int n_mask, int n, int dst_pitch, cudaStream_t stream);
 cudaError_t launch_reduce_partials(const ReduceParams& p, int dtype_is_bf16, cudaStream_t stream);
+cudaError_t ensure_context();
 cudaError_t launch_finalize(const float* partial, int dtype_is_bf16, int H, int N,
                             const void* logit_scale, void* dbias, void* dscale, cudaStream_t stream);
 
@@ -253,6 +254,10 @@ extern "C" int fwa2_forward(const fwa2_fwd_args* a, void* stream) {
   if (!aligned16(a->o.ptr)) return FWA2_ERR_ALIGN;
   if ((a->o.stride_n % 8) != 0 || (a->o.stride_h % 8) != 0 || (a->o.stride_bw % 8) != 0) return FWA2_ERR_STRIDE;
 
+  {
+    const cudaError_t ce = ensure_context();   // the tensor maps below are encoded by a driver call
+    if (ce != cudaSuccess) { g_last_cuda_error = static_cast<int>(ce); return FWA2_ERR_LAUNCH; }
+  }
   FwdParams p;
   std::memset(&p, 0, sizeof(p));
   if ((rc = encode_rows4(&p.tm_q, a->q, a->dtype, a->bw, a->heads, a->n)) != FWA2_OK) return rc;
@@ -360,6 +365,10 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
 
   const DeviceInfo dev = device_info();
   if (!dev.ok) return FWA2_ERR_LAUNCH;
+  {
+    const cudaError_t ce = ensure_context();   // the tensor maps below are encoded by a driver call
+    if (ce != cudaSuccess) { g_last_cuda_error = static_cast<int>(ce); return FWA2_ERR_LAUNCH; }
+  }
   const bool quad = wants_quad(a->n, a->variant);
   BwdPlan pl = make_bwd_plan(a->bw, a->heads, a->n, a->n_windows, has_bias, has_mask, dev.sm_count, quad);
   if (a->workspace == nullptr || a->workspace_bytes < pl.total ||

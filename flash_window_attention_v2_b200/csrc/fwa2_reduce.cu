@@ -155,6 +155,14 @@ __global__ void __launch_bounds__(256) finalize_kernel(const float* __restrict__
   }
 }
 
+// cuTensorMapEncodeTiled is a driver call and needs the device's primary context current on the
+// calling thread; a thread that has made no runtime call that touches the device yet (an autograd
+// worker entering the backward pass) may not have it.  Looking up a kernel's attributes binds it.
+cudaError_t ensure_context() {
+  cudaFuncAttributes attr;
+  return cudaFuncGetAttributes(&attr, transpose_tables_kernel);
+}
+
 cudaError_t launch_transpose_tables(const void* bias, long long bias_pitch, void* bias_t,
                                     const void* mask, long long mask_pitch, void* mask_t, int n_bias,
                                     int n_mask, int n, int dst_pitch, cudaStream_t stream) {
