@@ -17,8 +17,11 @@ import torch
 LN_100 = math.log(100.0)
 
 
-def forward_backward(q, k, v, do, logit_scale=None, bias=None, mask=None):
-    """fp32 CPU tensors in, dict(o, lse, dq, dk, dv, dbias, dscale) out."""
+def forward_backward(q, k, v, do, logit_scale=None, bias=None, mask=None, with_magnitude=False):
+    """fp32 CPU tensors in, dict(o, lse, dq, dk, dv, dbias, dscale) out.
+
+    with_magnitude: also return `dscale_mag`, the per-head sum of the ABSOLUTE values of the terms
+    dLogitScale adds up (the yardstick for its error when the signed sum nearly cancels)."""
     bw, h, n, d = q.shape
     qn = q.norm(dim=-1, keepdim=True).clamp_min(1e-12)
     kn = k.norm(dim=-1, keepdim=True).clamp_min(1e-12)
@@ -43,12 +46,14 @@ def forward_backward(q, k, v, do, logit_scale=None, bias=None, mask=None):
     ds = p * (dp - delta)
     dbias = ds.sum(0) if bias is not None else None
     dc = ds * s
-    dscale = None
+    dscale = dscale_mag = None
     if logit_scale is not None:
         gate = (logit_scale.reshape(h) <= LN_100).to(q.dtype)
         dscale = ((dc * c).sum(dim=(0, 2, 3)) * gate).reshape(h, 1, 1)
+        if with_magnitude:
+            dscale_mag = (dc * c).abs().sum(dim=(0, 2, 3))
     dqh = dc @ kh
     dkh = dc.transpose(-1, -2) @ qh
     dq = (dqh - qh * (qh * dqh).sum(-1, keepdim=True)) / qn
     dk = (dkh - kh * (kh * dkh).sum(-1, keepdim=True)) / kn
-    return dict(o=o, lse=lse, dq=dq, dk=dk, dv=dv, dbias=dbias, dscale=dscale)
+    return dict(o=o, lse=lse, dq=dq, dk=dk, dv=dv, dbias=dbias, dscale=dscale, dscale_mag=dscale_mag)
