@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libfwa2_b200.so")
 CSRC = os.path.join(HERE, "csrc")
 SOURCES = ["fwa2_api.cu", "fwa2_fwd.cu", "fwa2_bwd.cu", "fwa2_bwd_quad.cu", "fwa2_reduce.cu", "fwa2_selftest.cu",
-           "fwa2_static_scratch.cu", "fwa2_cpb_bias.cu"]
+           "fwa2_static_scratch.cu", "fwa2_cpb_bias.cu", "fwa2_peer_reduce.cu"]
 
 FWA2_ABI_VERSION = 1
 FWA2_F16, FWA2_BF16 = 0, 1
@@ -61,7 +61,7 @@ class BwdArgs(C.Structure):
 EXPORTS = ("fwa2_abi_version", "fwa2_strerror", "fwa2_last_cuda_error", "fwa2_forward",
            "fwa2_bwd_workspace_bytes", "fwa2_backward", "fwa2_finalize_grads",
            "fwa2_selftest_mma", "fwa2_selftest_mma_timing", "fwa2_backward_static_scratch",
-           "fwa2_cpb_bias_forward", "fwa2_cpb_bias_backward")
+           "fwa2_cpb_bias_forward", "fwa2_cpb_bias_backward", "fwa2_peer_reduce_finalize")
 
 
 def nvcc_command(out_path: str = LIB_PATH, verbose: bool = False):
@@ -125,6 +125,10 @@ def lib() -> C.CDLL:
         L.fwa2_cpb_bias_backward.restype = C.c_int
         L.fwa2_cpb_bias_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                              C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+        L.fwa2_peer_reduce_finalize.restype = C.c_int
+        L.fwa2_peer_reduce_finalize.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
+                                                C.c_uint32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                                C.c_void_p, C.c_void_p, C.c_void_p]
         L.fwa2_selftest_mma_timing.restype = C.c_int
         L.fwa2_selftest_mma_timing.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                C.c_void_p]

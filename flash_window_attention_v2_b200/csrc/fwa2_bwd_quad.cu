@@ -414,7 +414,6 @@ __device__ void quad_epilogue_role(const QuadParams& p, uint8_t* smem_ptr, uint3
   const bool quad = p.cluster > 1;
   const uint32_t half = lt >> 6;
   const bool keeper = quad ? (half == (g.a ^ g.b)) : true;   // finishes its rows of dV and dK
-  const bool fin_q = quad ? !keeper : true;                  // finishes its row of dQ
   const uint32_t recv_base = smem_base + p.off_recv;
   const uint32_t row64 = lt & 63u, row_sw = lt & 7u;
   const int krow = static_cast<int>(g.a * kTileRows + lt), qrow = static_cast<int>(g.b * kTileRows + lt);

@@ -14,6 +14,7 @@ own bias gradient and DDP averages parameter gradients; use the plain function.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -119,17 +120,76 @@ def sharded_flash_win_attn_v2_func(q, k, v, logit_scale=None, bias=None, mask=No
     return ShardedFlashWindowAttentionV2.apply(q, k, v, logit_scale, bias, mask, group)
 
 
+class PeerReducer:
+    """The cross-GPU sum of dBias / dLogitScale as ONE kernel per GPU over peer memory
+    (`fwa2_peer_reduce_finalize`): every rank's fp32 sums live in symmetric memory that all ranks
+    have mapped; the kernel exchanges one flag per peer, adds the buffers in rank order and casts.
+    Two buffer sets alternate from call to call (a fast rank may start the next step while a slow
+    one still reads this step's sums).  Raises at construction if symmetric memory is unavailable;
+    callers then stay on the NCCL all-reduce."""
+
+    def __init__(self, heads: int, n: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        import ctypes as C
+
+        import torch.distributed._symmetric_memory as symm
+        self._C = C
+        group = group if group is not None else dist.group.WORLD
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise RuntimeError("fwa2_peer_reduce_finalize is built for at most 8 peers")
+        self.heads, self.n = heads, n
+        numel = heads * n * n + heads
+        self.bufs = [symm.empty(numel, dtype=torch.float32, device=device) for _ in range(2)]
+        self.flags = symm.empty(64, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        for b in self.bufs:
+            b.zero_()
+        torch.cuda.synchronize(device)
+        name = group.group_name
+        self._hdls = [symm.rendezvous(b, name) for b in self.bufs]
+        self._hflag = symm.rendezvous(self.flags, name)
+        self._buf_ptrs = [(C.c_void_p * self.world)(*[int(p) for p in h.buffer_ptrs]) for h in self._hdls]
+        self._flag_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self._hflag.buffer_ptrs])
+        self._hflag.barrier()          # every rank's flags are zero before anybody writes one
+        self.epoch = 0
+
+    def next_buffer(self) -> torch.Tensor:
+        """The buffer the NEXT call of reduce() will read on this rank: hand it to the backward as
+        its `_partial_out`."""
+        return self.bufs[(self.epoch + 1) & 1]
+
+    def reduce(self, logit_scale, db, dscale) -> None:
+        """Sum over the ranks and cast into db / dscale (either may be None).  Stream-ordered after
+        the backward that filled next_buffer(); returns at once."""
+        from . import _lib, kernels
+        self.epoch += 1
+        ref = db if db is not None else dscale
+        with torch.cuda.device(ref.device):
+            _lib.check(_lib.lib().fwa2_peer_reduce_finalize(
+                self._buf_ptrs[self.epoch & 1], self._flag_ptrs, self.rank, self.world, self.epoch & 0xFFFFFFFF,
+                kernels._DTYPES[ref.dtype], self.heads, self.n,
+                logit_scale.data_ptr() if dscale is not None else None,
+                db.data_ptr() if db is not None else None, dscale.data_ptr() if dscale is not None else None,
+                kernels._status(ref.device).data_ptr(),
+                self._C.c_void_p(torch.cuda.current_stream(ref.device).cuda_stream)), "fwa2_peer_reduce_finalize")
+
+
 class GraphedShardedStep:
-    """Forward + backward of this rank's windows with the local kernels captured in a CUDA graph.
+    """Forward + backward of this rank's windows with the local kernels captured in CUDA graphs.
 
     The graph holds what needs no other rank (forward, backward, the local fp32 sums of dBias and
-    dLogitScale); the exchange step -- one NCCL all-reduce of `H*N*N + H` floats -- and the final
-    cast run outside it, so that nothing that can block on a peer is inside a capture.
-    Fill `.q .k .v .do` in place, call `replay()`, read `(o, dq, dk, dv, dscale, dbias)`."""
+    dLogitScale); the exchange step runs outside it, so that nothing that can block on a peer is
+    inside a capture: with a `PeerReducer` one fused kernel over peer memory (two graphs, one per
+    buffer set, replayed alternately), otherwise one NCCL all-reduce of `H*N*N + H` floats and the
+    cast kernel.  Fill `.q .k .v .do` in place, call `replay()`, read
+    `(o, dq, dk, dv, dscale, dbias)`."""
 
-    def __init__(self, q, k, v, do, logit_scale, bias, mask, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, q, k, v, do, logit_scale, bias, mask, group: Optional[dist.ProcessGroup] = None,
+                 reducer: Optional[PeerReducer] = None):
         dev = q.device
         self.group = group
+        self.reducer = reducer
         self.q, self.k, self.v, self.do = (x.detach().clone() for x in (q, k, v, do))
         self.logit_scale = logit_scale.detach().clone() if logit_scale is not None else None
         self.bias = bias.detach().clone() if bias is not None else None
@@ -139,31 +199,114 @@ class GraphedShardedStep:
         else:
             self.scale_type = "scalar"
             self._ls = torch.tensor(1.0 / math.sqrt(q.shape[-1]), device=dev)
+        self._need = self.bias is not None or self.scale_type == "tensor"
 
-        def local():
+        def local(partial):
+            from . import kernels
             o, lse, ls = CudaBackend.forward(self.q, self.k, self.v, self._ls, self.bias, self.mask, self.scale_type)
-            dq, dk, dv, partial = CudaBackend.backward_partial(self.do, self.q, self.k, self.v, ls, o, lse,
-                                                               self.bias, self.mask, self.scale_type)
-            return o, dq, dk, dv, partial
+            dq, dk, dv = torch.empty_like(self.q), torch.empty_like(self.k), torch.empty_like(self.v)
+            kernels._flash_attn_backward(self.do, self.q, self.k, self.v, ls, o, lse, dq, dk, dv, None, None,
+                                         bias=self.bias, mask=self.mask, scale_type=self.scale_type,
+                                         _partial_out=partial)
+            return o, dq, dk, dv
 
+        h, n = q.shape[1], q.shape[2]
+        if reducer is not None and self._need:
+            partials = list(reducer.bufs)
+        elif self._need:
+            partials = [torch.zeros(h * n * n + h, dtype=torch.float32, device=dev)]
+        else:
+            partials = [None]
+        self._partials = partials
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
+            scratch = torch.zeros(h * n * n + h, dtype=torch.float32, device=dev) if self._need else None
             for _ in range(2):
-                local()
+                local(scratch)       # warm-up must not touch buffers that peers may be reading
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.o, self.dq, self.dk, self.dv, self.partial = local()
+        self.graphs, self.outs = [], []
+        for pbuf in partials:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.outs.append(local(pbuf))
+            self.graphs.append(g)
+        self.db = torch.empty_like(self.bias) if self.bias is not None else None
+        self.dscale = torch.empty_like(self.logit_scale) if self.scale_type == "tensor" else None
 
     def replay(self):
         from . import kernels
         kernels.poll_device_status(self.q.device)
-        self.graph.replay()
+        if self.reducer is not None and self._need:
+            i = (self.reducer.epoch + 1) & 1
+            self.graphs[i].replay()
+            self.reducer.reduce(self._ls, self.db, self.dscale)
+            o, dq, dk, dv = self.outs[i]
+            return o, dq, dk, dv, self.dscale, self.db
+        self.graphs[0].replay()
+        o, dq, dk, dv = self.outs[0]
         db = dscale = None
-        if self.partial is not None:
+        if self._need:
+            partial = self._partials[0]
             if self.group is not None or (dist.is_initialized() and dist.get_world_size() > 1):
-                dist.all_reduce(self.partial, op=dist.ReduceOp.SUM, group=self.group)
-            db, dscale = CudaBackend.finalize(self.partial, self._ls, self.bias, self.scale_type)
-        return self.o, self.dq, self.dk, self.dv, dscale, db
+                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+            kernels.finalize_grads(partial, self._ls, self.db, self.dscale)
+            db, dscale = self.db, self.dscale
+        return o, dq, dk, dv, dscale, db
+
+
+def sharded_parity_check(w, device, reducer: Optional[PeerReducer] = None, images_per_rank: int = 1):
+    """Before a multi-GPU measurement: a small problem that every rank holds in full (same seed),
+    computed unsharded on this GPU with the plain function and sharded over the ranks; this rank's
+    slice of o / dq / dk / dv must agree bitwise (a window's results do not depend on which other
+    windows share the launch) and the summed dBias / dLogitScale to rounding.  Returns a dict with
+    the worst deviations over all ranks."""
+    from .flash_window_attention_v2 import flash_win_attn_v2_func
+    from .workloads import Workload, make_inputs
+    world, rank = dist.get_world_size(), dist.get_rank()
+    small = Workload(w.name + "_parity", batch=images_per_rank * world, nw=w.nw, heads=w.heads, window=w.window,
+                     dtype=w.dtype)
+    t = make_inputs(small, seed=1234, device=device)
+    q, k, v = (t[x].detach().requires_grad_(True) for x in ("q", "k", "v"))
+    ls, bias = t["logit_scale"].detach().requires_grad_(True), t["bias"].detach().requires_grad_(True)
+    o = flash_win_attn_v2_func(q, k, v, ls, bias, t["mask"])
+    ref = (o,) + torch.autograd.grad(o, (q, k, v, ls, bias), t["do"])
+    sl = window_slice(small.batch, small.nw, world, rank)
+    step = GraphedShardedStep(t["q"][sl], t["k"][sl], t["v"][sl], t["do"][sl], t["logit_scale"], t["bias"], t["mask"],
+                              reducer=reducer)
+    so, sdq, sdk, sdv, sds, sdb = step.replay()
+    torch.cuda.synchronize(device)
+    exact = all(torch.equal(a, b[sl]) for a, b in zip((so, sdq, sdk, sdv), ref[:4]))
+    rel = lambda a, b: float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30))
+    dev_db, dev_ds = rel(sdb, ref[5]), rel(sds, ref[4])
+    stats = torch.tensor([0.0 if exact else 1.0, dev_db, dev_ds], device=device)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    # every rank must also hold the SAME summed gradients, bit for bit
+    mine = torch.cat([sdb.float().reshape(-1), sds.float().reshape(-1)])
+    lo, hi = mine.clone(), mine.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    return dict(images=small.batch, window_results_bitwise_equal=bool(stats[0].item() == 0.0),
+                dbias_rel_dev=float(stats[1]), dscale_rel_dev=float(stats[2]),
+                sums_identical_on_all_ranks=bool(torch.equal(lo, hi)))
+
+
+def make_sharded_step(t, w, device, kernels_module=None):
+    """What bench.py times on N > 1 GPUs: this rank's share of the images, local kernels replayed
+    from CUDA graphs, then the cross-GPU sum of dBias / dLogitScale -- the fused peer-memory kernel
+    when symmetric memory can be set up, the NCCL all-reduce otherwise.  Returns
+    (step, parity_report, description)."""
+    reducer = None
+    why = ""
+    if os.environ.get("FWA2_SHARDED_EXCHANGE", "peer") == "peer":
+        try:
+            reducer = PeerReducer(t["q"].shape[1], t["q"].shape[2], device)
+        except Exception as ex:      # no symmetric memory on this system: say so, use NCCL
+            why = f" (peer-memory exchange unavailable: {type(ex).__name__}: {ex})"
+    parity = sharded_parity_check(w, device, reducer)
+    step = GraphedShardedStep(t["q"], t["k"], t["v"], t["do"], t["logit_scale"], t["bias"], t["mask"], reducer=reducer)
+    api = ("GraphedShardedStep: local kernels replayed from a CUDA graph, then " +
+           ("one fused peer-memory kernel (fwa2_peer_reduce_finalize over NVLink) for the sum of dBias / dLogitScale"
+            if reducer is not None else "NCCL all-reduce + cast of dBias / dLogitScale" + why))
+    return step.replay, parity, api

@@ -126,3 +126,22 @@ def make_inputs(w: Workload, seed: int = 0, device="cpu", batch: int | None = No
     if device != "cpu":
         out = {k_: (t.to(device) if t is not None else None) for k_, t in out.items()}
     return out
+
+
+def make_reference_recipe_inputs(w: Workload, seed: int = 0, device="cpu"):
+    """Inputs drawn the way the reference's own attention benchmark draws them
+    (benchmark/bench_attn.py:20-30): q, k, v, bias and logit_scale ~ N(0, 1), a mask that is -inf
+    where an independent N(0, 1) draw is negative and 0 elsewhere, and an upstream gradient of -1
+    everywhere (its loss is `-out.sum()`).  Same dict as `make_inputs`."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    dt = TORCH_DTYPES[w.dtype]
+    shape = (w.bw, w.heads, w.n, w.head_dim)
+    out = {name: torch.randn(shape, generator=gen).to(dt) for name in ("q", "k", "v")}
+    out["bias"] = torch.randn(w.heads, w.n, w.n, generator=gen).to(dt)
+    draw = torch.randn(w.nw, w.n, w.n, generator=gen)
+    out["mask"] = torch.zeros(w.nw, w.n, w.n).masked_fill(draw < 0, float("-inf")).to(dt)
+    out["logit_scale"] = torch.randn(w.heads, 1, 1, generator=gen).to(dt)
+    out["do"] = torch.full(shape, -1.0).to(dt)
+    if device != "cpu":
+        out = {k_: t.to(device) for k_, t in out.items()}
+    return out

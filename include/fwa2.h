@@ -141,6 +141,21 @@ int fwa2_backward(const fwa2_bwd_args* args, void* stream);
 int fwa2_finalize_grads(const float* partial, int32_t dtype, int32_t heads, int32_t n,
                         const void* logit_scale, void* dbias, void* dscale, void* stream);
 
+/* The exchange step of the window-sharded backward (one process per GPU, windows split over the
+ * GPUs) as one kernel per GPU over peer memory: sums every rank's fp32 [H*N*N dBias | H
+ * dLogitScale] buffer in ascending rank order and applies fwa2_finalize_grads' gate and cast.
+ * Stands where the reference would need an all-reduce of its fp32 accumulators followed by the
+ * casts of attn_kernel_backward.py:703-711 (the reference itself has no multi-GPU path).
+ * partials[r] / flags[r]: rank r's buffer and rank r's flag array (at least 8 zero-initialised
+ * uint32, written only by this call) as mapped into THIS process (symmetric / peer memory).
+ * epoch: 1, 2, 3, ... the same sequence on every rank; consecutive epochs must use different
+ * `partials` buffers (two sets, alternating).  Waits for the peers are bounded (about a second);
+ * on expiry `status` is written, the outputs are not.  Every rank must make the matching call. */
+int fwa2_peer_reduce_finalize(const float* const* partials, uint32_t* const* flags, int32_t rank,
+                              int32_t world, uint32_t epoch, int32_t dtype, int32_t heads, int32_t n,
+                              const void* logit_scale, void* dbias, void* dscale, void* status,
+                              void* stream);
+
 /* The step in front of the operator in Swin-V2 (swin_transformer_v2.py:283-287), fused into one
  * kernel:  bias[h, i, j] = 16 * sigmoid(table[index[i, j], h]).
  * table: (rows, heads), fp32 when table_is_f32 else `dtype`; index: (n, n) int32 with values in
