@@ -36,7 +36,7 @@ class FwdArgs(C.Structure):
         ("bias", C.c_void_p), ("mask", C.c_void_p),
         ("bias_row_stride", C.c_int64), ("mask_row_stride", C.c_int64),
         ("status", C.c_void_p), ("variant", C.c_int32), ("max_ctas", C.c_int32),
-        ("trace", C.c_void_p), ("trace_entries", C.c_int32), ("reserved0", C.c_int32),
+        ("developer0", C.c_void_p), ("developer1", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 
@@ -54,13 +54,13 @@ class BwdArgs(C.Structure):
         ("dbias", C.c_void_p), ("dscale", C.c_void_p), ("partial_out", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p), ("variant", C.c_int32), ("max_ctas", C.c_int32),
-        ("trace", C.c_void_p), ("trace_entries", C.c_int32), ("reserved0", C.c_int32),
+        ("developer0", C.c_void_p), ("developer1", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 
 EXPORTS = ("fwa2_abi_version", "fwa2_strerror", "fwa2_last_cuda_error", "fwa2_forward",
            "fwa2_bwd_workspace_bytes", "fwa2_backward", "fwa2_finalize_grads",
-           "fwa2_selftest_mma", "fwa2_selftest_mma_timing", "fwa2_backward_static_scratch",
+           "fwa2_selftest_mma", "fwa2_backward_static_scratch",
            "fwa2_cpb_bias_forward", "fwa2_cpb_bias_backward", "fwa2_peer_reduce_finalize")
 
 
@@ -129,9 +129,6 @@ def lib() -> C.CDLL:
         L.fwa2_peer_reduce_finalize.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
                                                 C.c_uint32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                                 C.c_void_p, C.c_void_p, C.c_void_p]
-        L.fwa2_selftest_mma_timing.restype = C.c_int
-        L.fwa2_selftest_mma_timing.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
-                                               C.c_void_p]
         if L.fwa2_abi_version() != FWA2_ABI_VERSION:
             raise RuntimeError("libfwa2_b200.so ABI version mismatch; rebuild it")
         _lib = L

@@ -36,7 +36,9 @@ def inverse_index(index: torch.Tensor, rows: int):
     counts = torch.bincount(flat, minlength=rows)
     offsets = torch.zeros(rows + 1, dtype=torch.int32, device=index.device)
     offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
-    _inverse_cache.clear()
+    # one entry per index buffer (every Swin block has its own), oldest dropped beyond 64
+    if len(_inverse_cache) >= 64:
+        _inverse_cache.pop(next(iter(_inverse_cache)))
     _inverse_cache[key] = (offsets, order)
     return offsets, order
 

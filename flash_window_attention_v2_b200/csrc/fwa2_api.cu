@@ -26,6 +26,13 @@ cudaError_t launch_finalize(const float* partial, int dtype_is_bf16, int H, int 
 
 namespace {
 
+// development builds only: leave dBias out of the backward (timing experiments)
+#ifdef FWA2_DEVELOPER
+constexpr int kSkipDbias = 8;
+#else
+constexpr int kSkipDbias = 0;
+#endif
+
 thread_local int g_last_cuda_error = 0;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -219,6 +226,11 @@ int cached_max_clusters(int dtype_is_bf16, int cluster, uint32_t smem_bytes) {
 }  // namespace
 }  // namespace fwa2
 
+namespace fwa2 {
+// for the other translation units of the library: what fwa2_last_cuda_error() reports
+void set_last_cuda_error(int e) { g_last_cuda_error = e; }
+}  // namespace fwa2
+
 using namespace fwa2;
 
 extern "C" int fwa2_abi_version(void) { return FWA2_ABI_VERSION; }
@@ -283,8 +295,8 @@ extern "C" int fwa2_forward(const fwa2_fwd_args* a, void* stream) {
   const int units = a->bw * a->heads;
   p.n_jobs = p.pair_mode ? (units + 1) / 2 : units;
   p.status = static_cast<DeviceStatus*>(a->status);
-  p.trace.buf = reinterpret_cast<unsigned long long*>(a->trace);
-  p.trace.cap = a->trace != nullptr ? a->trace_entries : 0;
+  p.trace.buf = reinterpret_cast<unsigned long long*>(a->developer0);
+  p.trace.cap = a->developer0 != nullptr ? a->developer1 : 0;
 
   // ---- shared memory layout: prefer two CTAs per SM ----
   const bool p_in_tmem = (a->variant & FWA2_FWD_P_IN_SMEM) == 0;
@@ -377,7 +389,7 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   void* bias_t = ws + pl.off_bias_t;
   void* mask_t = ws + pl.off_mask_t;
-  float* db_partial = (has_bias && (a->variant & FWA2_BWD_SKIP_DBIAS) == 0) ? reinterpret_cast<float*>(ws + pl.off_db) : nullptr;
+  float* db_partial = (has_bias && (a->variant & kSkipDbias) == 0) ? reinterpret_cast<float*>(ws + pl.off_db) : nullptr;
   float* dscale_partial = reinterpret_cast<float*>(ws + pl.off_dscale);
 
   // Everything that can fail is checked and every descriptor is encoded before the first launch:
@@ -412,7 +424,7 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
     qp.has_bias = has_bias; qp.has_mask = has_mask;
     qp.cluster = pl.cluster;
     qp.status = static_cast<DeviceStatus*>(a->status);
-    qp.prof = (a->trace != nullptr && a->trace_entries >= 64) ? reinterpret_cast<unsigned long long*>(a->trace) : nullptr;
+    qp.prof = (a->developer0 != nullptr && a->developer1 >= 64) ? reinterpret_cast<unsigned long long*>(a->developer0) : nullptr;
     if (!quad_smem_plan(qp, static_cast<uint32_t>(dev.max_smem_optin))) return FWA2_ERR_SHAPE;
     // no more clusters than the device holds at once (fewer clusters use a prefix of the
     // workspace's partial buffers)
@@ -461,8 +473,8 @@ extern "C" int fwa2_backward(const fwa2_bwd_args* a, void* stream_v) {
     p.pair_mode = pl.pair;
     p.nslots = pl.nslots;
     p.status = static_cast<DeviceStatus*>(a->status);
-    p.trace.buf = reinterpret_cast<unsigned long long*>(a->trace);
-    p.trace.cap = a->trace != nullptr ? a->trace_entries : 0;
+    p.trace.buf = reinterpret_cast<unsigned long long*>(a->developer0);
+    p.trace.cap = a->developer0 != nullptr ? a->developer1 : 0;
 
     // ---- shared memory layout (one CTA per SM) ----
     p.rows_kv = pl.pair ? 128 : ((a->n + 127) / 128) * 128;

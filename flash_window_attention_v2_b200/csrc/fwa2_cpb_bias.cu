@@ -65,11 +65,16 @@ __global__ void __launch_bounds__(256) cpb_bias_bwd_kernel(const float* __restri
   const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (r >= rows) return;
-  const int beg = offsets[r], end = offsets[r + 1];
+  // a malformed inverse index must not become an out-of-range read: offsets are clamped to the
+  // list, positions outside the (n, n) table are skipped
+  const int beg = max(0, min(offsets[r], nn)), end = max(beg, min(offsets[r + 1], nn));
   for (int h = 0; h < heads; ++h) {
     const float* src = dbias + static_cast<long long>(h) * nn;
     float acc = 0.f;
-    for (int p = beg + lane; p < end; p += 32) acc += src[positions[p]];
+    for (int p = beg + lane; p < end; p += 32) {
+      const int pos = positions[p];
+      if (static_cast<unsigned>(pos) < static_cast<unsigned>(nn)) acc += src[pos];
+    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
     if (lane == 0) {
@@ -79,7 +84,9 @@ __global__ void __launch_bounds__(256) cpb_bias_bwd_kernel(const float* __restri
   }
 }
 
-thread_local int g_cpb_last_error = 0;
+}  // namespace
+namespace fwa2 { void set_last_cuda_error(int e); }
+namespace {
 
 }  // namespace
 
@@ -107,7 +114,7 @@ extern "C" int fwa2_cpb_bias_forward(const void* table, int32_t table_is_f32, co
           static_cast<const __nv_bfloat16*>(table), index, nn, heads, rows, static_cast<__nv_bfloat16*>(bias));
   }
   const cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) { g_cpb_last_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
+  if (e != cudaSuccess) { fwa2::set_last_cuda_error(static_cast<int>(e)); return FWA2_ERR_LAUNCH; }
   return FWA2_OK;
 }
 
@@ -132,6 +139,6 @@ extern "C" int fwa2_cpb_bias_backward(const float* dbias_f32, const void* table,
     cpb_bias_bwd_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(dbias_f32, static_cast<const __nv_bfloat16*>(table),
                                                                row_offsets, positions, nn, heads, rows, dtable_f32);
   const cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) { g_cpb_last_error = static_cast<int>(e); return FWA2_ERR_LAUNCH; }
+  if (e != cudaSuccess) { fwa2::set_last_cuda_error(static_cast<int>(e)); return FWA2_ERR_LAUNCH; }
   return FWA2_OK;
 }

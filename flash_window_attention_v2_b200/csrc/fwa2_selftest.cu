@@ -243,6 +243,8 @@ mma_timing_kernel(int n, int a_tmem, int chains, int count, float* __restrict__ 
 
 }  // namespace fwa2
 
+// (development builds only: a micro-benchmark of the tcgen05.mma issue rate)
+#ifdef FWA2_DEVELOPER
 extern "C" int fwa2_selftest_mma_timing(int n, int a_tmem, int chains, int count, float* out,
                                         void* status, void* stream) {
   using namespace fwa2;
@@ -257,9 +259,12 @@ extern "C" int fwa2_selftest_mma_timing(int n, int a_tmem, int chains, int count
   return e == cudaSuccess ? 0 : -100 - static_cast<int>(e);
 }
 
+#endif  // FWA2_DEVELOPER
+
 extern "C" int fwa2_selftest_mma(int mode, int dtype, const void* a, const void* b, float* d,
                                  void* status, void* stream) {
   using namespace fwa2;
+  if (a == nullptr || b == nullptr || d == nullptr) return -1;   // FWA2_ERR_NULL: never reaches the device
   if (mode < 0 || mode > 3 || (dtype != 0 && dtype != 1)) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t smem = 32768 + 8192 + 1024;

@@ -131,6 +131,7 @@ def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="
     assert k.shape == (batch_window_size, n_heads, seqlen_k, d)
     assert v.shape == (batch_window_size, n_heads, seqlen_k, d)
     assert d <= 128, "FlashAttention only support head dimensions up to 128"
+    assert d == 32, "this library is built for head dimension 32 (every Swin-V2 configuration uses it)"
     assert q.dtype == k.dtype == v.dtype, "All tensors must have the same type"
     assert q.dtype in [torch.float16, torch.bfloat16], "Only support fp16 and bf16"
     assert q.is_cuda and k.is_cuda and v.is_cuda and logit_scale.is_cuda
@@ -182,9 +183,9 @@ def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="
     a.status = _status(q.device).data_ptr()
     a.variant = _variant
     a.max_ctas = _max_ctas
-    if _trace is not None:      # int64 tensor of 4 * entries words: timeline of CTA 0
-        a.trace = _trace.data_ptr()
-        a.trace_entries = _trace.numel() // 4
+    if _trace is not None:      # development builds of the library only
+        a.developer0 = _trace.data_ptr()
+        a.developer1 = _trace.numel() // 4
     with torch.cuda.device(q.device):
         _lib.check(_lib.lib().fwa2_forward(C.byref(a), _stream(q.device)), "fwa2_forward")
     return o, lse, logit_scale
@@ -205,6 +206,7 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
     batch_window_size, n_heads, seqlen_q, d = q.shape
     _, _, seqlen_k, _ = k.shape
     assert d <= 128
+    assert d == 32, "this library is built for head dimension 32 (every Swin-V2 configuration uses it)"
     assert seqlen_q == seqlen_k
     seqlen_q_rounded = math.ceil(seqlen_q / 64) * 64
     assert lse.shape == (batch_window_size, n_heads, seqlen_q_rounded)
@@ -272,9 +274,9 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
         a.status = _status(q.device).data_ptr()
         a.variant = _variant
         a.max_ctas = _max_ctas
-        if _trace is not None:
-            a.trace = _trace.data_ptr()
-            a.trace_entries = _trace.numel() // 4
+        if _trace is not None:      # development builds of the library only
+            a.developer0 = _trace.data_ptr()
+            a.developer1 = _trace.numel() // 4
         _lib.check(L.fwa2_backward(C.byref(a), _stream(q.device)), "fwa2_backward")
         _mirror_status(q.device)
 

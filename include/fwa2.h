@@ -1,10 +1,17 @@
 /* C ABI of the B200 window-attention library (libfwa2_b200.so).
  *
  * Plain pointers and sizes only; no torch types.  Every device buffer, including the
- * workspace, is owned by the caller; the library allocates no device memory and keeps no
- * mutable global state.  All entry points return 0 on success and a negative code on error
- * (see fwa2_strerror); nothing is launched when an argument check fails.  No entry point
- * synchronises the host with the device, so calls may be captured in a CUDA graph.
+ * workspace, is owned by the caller; the library allocates no device memory.  The state it keeps
+ * is: a per-thread "last CUDA error", a host-side table of how many thread-block clusters each
+ * device holds at once, and -- for fwa2_backward_static_scratch only -- one fixed scratch array
+ * in its device image with the per-device address of that array.  All entry points return 0 on
+ * success and a negative code on error (see fwa2_strerror); every argument check and every
+ * descriptor is done before the first launch, so a rejected call launches nothing and leaves
+ * workspace and outputs untouched.  No entry point synchronises the host with the device.
+ *
+ * A kernel whose bounded device-side wait runs out writes the `status` block and returns with its
+ * outputs incomplete; callers of this raw ABI must look at that block (for example by copying it
+ * to the host after each step).
  *
  * The two compute entry points are what a binding for the reference project's kernel package
  * (flash_win_attn_v2/kernels/__init__.py:1-2) calls in place of its Triton launches.
@@ -45,8 +52,6 @@ enum fwa2_error {
 #define FWA2_BWD_SKIP_TABLES 2   /* backward: the workspace still holds the transposed tables of an
                                     identical earlier call (used to time the main kernel alone) */
 #define FWA2_BWD_SKIP_REDUCE 4   /* backward: leave the per-CTA partials in the workspace */
-#define FWA2_BWD_SKIP_DBIAS 8    /* backward, timing experiments only: do not accumulate dBias
-                                    (dbias then holds garbage) */
 #define FWA2_BWD_GENERAL_KERNEL 16 /* backward: windows of 65 to 256 tokens normally run on the
                                     cluster kernel (one 128 x 128 score tile per CTA); this bit
                                     selects the general kernel for them instead */
@@ -80,10 +85,8 @@ typedef struct fwa2_fwd_args {
                                timeout (must be zero-initialised by the caller); may be NULL */
   int32_t variant;          /* FWA2_FWD_* bits */
   int32_t max_ctas;         /* 0 = default (fill the device); otherwise an upper bound on the grid */
-  uint64_t* trace;          /* optional device buffer of 4 * trace_entries words: CTA 0 records a
-                               timeline there, one region per role, each word = (clock64 << 8) | event
-                               id; NULL = no tracing */
-  int32_t trace_entries;
+  uint64_t* developer0;     /* must be NULL (read only by development builds of the library) */
+  int32_t developer1;       /* must be 0 */
   int32_t reserved0;
 } fwa2_fwd_args;
 
@@ -116,8 +119,8 @@ typedef struct fwa2_bwd_args {
   void* status;
   int32_t variant;          /* FWA2_BWD_* bits */
   int32_t max_ctas;
-  uint64_t* trace;          /* as in fwa2_fwd_args */
-  int32_t trace_entries;
+  uint64_t* developer0;     /* must be NULL (read only by development builds of the library) */
+  int32_t developer1;       /* must be 0 */
   int32_t reserved0;
 } fwa2_bwd_args;
 
@@ -197,11 +200,6 @@ int fwa2_backward_static_scratch(const fwa2_bwd_args* args, void* stream);
 /* Device self-checks of the tensor-core building blocks (used by the test-suite). */
 int fwa2_selftest_mma(int mode, int dtype, const void* a, const void* b, float* d, void* status,
                       void* stream);
-
-/* Device micro-benchmark: cycles to issue, and to complete, `count` back-to-back tcgen05.mma of
- * shape 128 x n x 16 alternating between `chains` accumulators; out[0] = issue, out[1] = done. */
-int fwa2_selftest_mma_timing(int n, int a_tmem, int chains, int count, float* out, void* status,
-                             void* stream);
 
 #ifdef __cplusplus
 }

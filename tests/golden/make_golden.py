@@ -60,7 +60,9 @@ def build_inputs(name: str):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path of the reference checkout>")
+    ref_root = sys.argv[1]
     sys.path.insert(0, ref_root)
     from flash_win_attn_v2.win_attention_func import win_attention_torch  # the reference oracle
 

@@ -78,3 +78,12 @@ def test_workspace_size_formula(lib):
     assert 0 < small < big and nobias < big
     # 147 partial buffers of 256 x 256 fp32 dominate
     assert big >= 147 * 256 * 256 * 4
+
+
+def test_entry_points_reject_null_buffers_on_the_host(lib):
+    """A null pointer must come back as an error code, never reach a kernel."""
+    assert lib.fwa2_selftest_mma(0, 1, None, None, None, None, None) == -1
+    assert lib.fwa2_finalize_grads(None, 1, 3, 64, None, None, None, None) == -1
+    arr = (C.c_void_p * 2)(None, None)
+    assert lib.fwa2_peer_reduce_finalize(arr, arr, 0, 2, 1, 1, 3, 64, None, None, None, None, None) == -1
+    assert lib.fwa2_peer_reduce_finalize(arr, arr, 0, 9, 1, 1, 3, 64, None, None, None, None, None) == -4
