@@ -258,6 +258,59 @@ def run_reference(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_triton(args, w):
+    """The reference's OWN Triton kernels on this GPU, untouched (no install()): fwd + bwd time on
+    `w` and their error against the fp32 oracle on a small sample -- the bar to beat on the same
+    box and the yardstick for this library's tolerances.  Returns a dict (with "unavailable" when
+    the reference is not installed or its kernels do not compile for this GPU)."""
+    if not os.path.isdir(os.path.join(REF_DIR, "flash_win_attn_v2")):
+        return dict(impl="reference-triton", unavailable="the reference project is not installed under baseline/_ref")
+    try:
+        if REF_DIR not in sys.path:
+            sys.path.insert(0, REF_DIR)
+        import numpy as np
+        from flash_win_attn_v2 import flash_win_attn_v2_func as ref_func
+        from oracle import window_attention_oracle as orc
+        dev = torch.device("cuda", 0)
+        out = dict(impl="reference-triton", workload=w.name, dtype=w.dtype)
+
+        def run(t):
+            q, k, v = (t[x].detach().requires_grad_(True) for x in ("q", "k", "v"))
+            ls, bias = t["logit_scale"].detach().requires_grad_(True), t["bias"].detach().requires_grad_(True)
+            o = ref_func(q, k, v, ls, bias, t["mask"])
+            return (o,) + torch.autograd.grad(o, (q, k, v, ls, bias), t["do"])
+
+        # error against the fp32 oracle: two images of the workload's geometry
+        small = Workload(w.name + "_sample", batch=2, nw=w.nw, heads=w.heads, window=w.window, dtype=w.dtype)
+        ts = make_inputs(small, seed=0, device=dev)
+        got = run(ts)
+        f = lambda x: x.detach().float().cpu().numpy()
+        ref = orc.forward_backward(*(f(ts[x]) for x in ("q", "k", "v", "do", "logit_scale", "bias", "mask")),
+                                   dtype=np.float32)
+        out["rel_err_vs_fp32_oracle"] = {name: float(orc.rel_err(f(g).reshape(ref[name].shape), ref[name]))
+                                         for name, g in zip(("o", "dq", "dk", "dv", "dscale", "dbias"), got)}
+        # time on the full workload
+        t = make_inputs(w, seed=0, device=dev)
+        for _ in range(3):
+            run(t)
+        torch.cuda.synchronize()
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        evs = []
+        for _ in range(max(3, min(args.steps, 10))):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            run(t)
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+        out.update(ms_per_step=ms, tflops=w.matmul_flops() / (ms * 1e-3) / 1e12)
+        return out
+    except Exception as ex:
+        return dict(impl="reference-triton", unavailable=f"{type(ex).__name__}: {str(ex)[:300]}")
+
+
 # ------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -265,7 +318,9 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="cfg4", help="cfg2 | cfg3 | cfg4 | sweep_w<window>")
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-triton"],
+                    help="reference: the classic path on the host cores; reference-triton: the reference's own "
+                         "Triton kernels on this GPU (same-box yardstick, needs baseline/_ref)")
     ap.add_argument("--inputs", default="standard", choices=["standard", "reference_recipe"],
                     help="reference_recipe: the value distributions of the reference's own attention benchmark")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -279,6 +334,10 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, w, rank)
+        return
+    if args.impl == "reference-triton":
+        if rank == 0:
+            print(json.dumps(run_reference_triton(args, w)), flush=True)
         return
 
     import torch.distributed as dist
@@ -501,6 +560,15 @@ def main():
         K.check_device_status(dev)
     if model is not None:
         extra["swinv2_b_train_step"] = model
+    if not args.no_extra and world == 1:
+        # the reference's own Triton kernels on this box, in a process of their own
+        for name in ("cfg3", "cfg4"):
+            try:
+                res = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-triton",
+                                      "--config", name, "--steps", "6"], capture_output=True, text=True, timeout=600)
+                extra[f"reference_triton_{name}"] = json.loads(res.stdout.strip().splitlines()[-1])
+            except Exception as ex:
+                extra[f"reference_triton_{name}"] = dict(unavailable=f"{type(ex).__name__}: {str(ex)[:200]}")
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:

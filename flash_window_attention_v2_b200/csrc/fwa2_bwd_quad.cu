@@ -20,9 +20,10 @@
 // also goes through shared memory for dQ^ += dS K^.
 //
 // Roles (640 threads): warps 0-3 / 4-7 compute warpgroups (step 0 / 1 of the tile, thread = key),
-// warps 8-11 epilogue warpgroup (the exchange and the epilogues, one job behind), warps 12-15
-// preparing warpgroup (normalises K and Q rows in place, delta, lse, one job ahead), warp 16
-// issues every tcgen05.mma, warp 17 is the TMA producer.
+// warps 8-11 epilogue warpgroup (exchange and epilogues of dV and dK, one job behind), warps 12-15
+// preparing warpgroup (normalises K and Q rows in place, delta, lse, up to two jobs ahead; in its
+// idle time the exchange and epilogue of dQ), warp 16 issues every tcgen05.mma, warp 17 is the TMA
+// producer.
 // Replaces flash_win_attn_v2/kernels/attn_kernel_backward.py:6-51 and :84-564 for these sizes.
 #define FWA2_NORMALISE_ROLLED 1
 #define FWA2_WAIT_INLINE 1
@@ -319,18 +320,114 @@ __device__ void quad_compute_role(const QuadParams& p, uint8_t* smem_ptr, uint32
 }
 
 // ------------------------------------------------------------------------------------------------
-// The preparing warpgroup (thread = row), ahead of the compute warpgroups: K row and Q row of a
-// job normalised in place, delta = dO . O and lse * log2(e) of the query row.
+// One row of one accumulator of one job (0 dV, 1 dK, 2 dQ), already in registers: either pushed
+// to the partner CTA that finishes it, or finished here -- the partner's term added, the Jacobian
+// of the L2 normalisation applied (dK^, dQ^), the row stored.
+// Row r of an accumulator is tensor-memory lane r.  Of dV and dK (rows = keys of block a; the
+// other term of the sum is held by CTA (a, 1 - b) = rank ^ 1) a CTA keeps the rows of half
+// f = a ^ b and pushes the other half to that partner; of dQ (rows = queries of tile b; partner
+// (1 - a, b) = rank ^ 2) it keeps half 1 - f.  A sum of two floats does not depend on the order,
+// so the results are bitwise reproducible.
+// ------------------------------------------------------------------------------------------------
+struct QuadRowCtx {
+  uint32_t bars, recv_base, rank, row64, row_sw, par;
+  bool quad;
+  float scale;
+};
+template <typename T>
+__device__ __forceinline__ bool quad_row(const QuadRowCtx& c, const WaitCtx& ctx, uint32_t (&r)[32], uint32_t X,
+                                         bool push, const uint4 (&raw)[4], bool ok, uint16_t* dst,
+                                         float& dscale_acc) {
+  const uint32_t partner = c.rank ^ (X == 2u ? 2u : 1u);
+  const uint32_t full = c.bars + 8u * (qbRecvFull + X), free_ = c.bars + 8u * (qbRecvFree + X);
+  const uint32_t slot = c.recv_base + X * kQRecvPart + c.row64 * 128u;
+  if (push) {
+    // the partner has read what I pushed for the previous job; each 16-byte piece credits the
+    // partner's barrier when it has landed there
+    if (!qwait<true>(free_, c.par ^ 1u, ctx, 58)) return false;
+    const uint32_t dst_row = cluster_map(slot, partner), dst_bar = cluster_map(full, partner);
+#pragma unroll
+    for (uint32_t ch = 0; ch < 8u; ++ch) st_async_cluster_v4(dst_row + ((ch ^ c.row_sw) << 4), &r[4 * ch], dst_bar);
+    return true;
+  }
+  if (c.quad) {
+    if (!qwait<true>(full, c.par, ctx, 59)) return false;
+#pragma unroll
+    for (uint32_t ch = 0; ch < 8u; ++ch) {
+      uint32_t w4[4];
+      lds128(slot + ((ch ^ c.row_sw) << 4), w4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        r[4 * ch + i] = __float_as_uint(__uint_as_float(r[4 * ch + i]) + __uint_as_float(w4[i]));
+    }
+    // (the additions above have consumed every loaded value: the buffer may be overwritten)
+    mbar_arrive_cluster_relaxed(cluster_map(free_, partner));
+  }
+  // rows of dV are stored as they are; rows of dK^ / dQ^ go through the Jacobian:
+  // dx = scale (dX' - x^ (x^ . dX')) / |x| from the raw row x
+  float fmul = 1.f, cq = 0.f;
+  if (X != 0u) {
+    float ss = 0.f, qd = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+      const uint32_t w4[4] = {raw[ch].x, raw[ch].y, raw[ch].z, raw[ch].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x0 = Elem<T>::lo(w4[e]), x1 = Elem<T>::hi(w4[e]);
+        ss = fmaf(x0, x0, ss);
+        ss = fmaf(x1, x1, ss);
+        qd = fmaf(x0, __uint_as_float(r[8 * ch + 2 * e]), qd);
+        qd = fmaf(x1, __uint_as_float(r[8 * ch + 2 * e + 1]), qd);
+      }
+    }
+    const float rn = rsqrtf(fmaxf(ss, 1e-24f));
+    const float dot = qd * rn;
+    if (X == 2u && ok) dscale_acc += dot;
+    fmul = c.scale * rn;
+    cq = rn * dot;
+  }
+  if (ok) {
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+      const uint32_t w4[4] = {raw[ch].x, raw[ch].y, raw[ch].z, raw[ch].w};
+      uint32_t o4[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v0 = __uint_as_float(r[8 * ch + 2 * e]), v1 = __uint_as_float(r[8 * ch + 2 * e + 1]);
+        if (X != 0u) {
+          v0 = fmul * (v0 - Elem<T>::lo(w4[e]) * cq);
+          v1 = fmul * (v1 - Elem<T>::hi(w4[e]) * cq);
+        }
+        o4[e] = Elem<T>::pack(v0, v1);
+      }
+      *reinterpret_cast<uint4*>(dst + 8 * ch) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+    }
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------
+// The preparing warpgroup (thread = row).  Ahead of the compute warpgroups: K row and Q row of a
+// job normalised in place, delta = dO . O and lse * log2(e) of the query row.  Behind them, in
+// the time it would otherwise wait for the next tiles to arrive: the dQ accumulator of the job
+// that has just finished (pushed to the partner by a keeper of dV / dK, finished by the others).
 // ------------------------------------------------------------------------------------------------
 template <typename T>
 __device__ void quad_prepare_role(const QuadParams& p, uint8_t* smem_ptr, uint32_t smem_base,
-                                  uint32_t bars, const WaitCtx& ctx, uint32_t rank) {
+                                  uint32_t bars, uint32_t tmem, const WaitCtx& ctx, uint32_t rank,
+                                  float& dscale_acc) {
   const QuadGeom g = quad_geom(p, rank);
   if (g.count == 0) return;
   const uint32_t lt = threadIdx.x & 127u;
+  const uint32_t lane_base = ((lt >> 5) * 32u) << 16;
   float* rowstats = reinterpret_cast<float*>(smem_ptr + p.off_rowstats);
   const int ig = static_cast<int>(g.b * kTileRows + lt);
   const bool row_ok = ig < p.N;
+  const bool quad = p.cluster > 1;
+  const bool keeper = quad ? ((lt >> 6) == (g.a ^ g.b)) : false;   // pushes its row of dQ
+  QuadRowCtx rc;
+  rc.bars = bars; rc.recv_base = smem_base + p.off_recv; rc.rank = rank; rc.row64 = lt & 63u; rc.row_sw = lt & 7u;
+  rc.quad = quad; rc.scale = load_scale<T>(p.scale, p.scale_is_tensor, g.h);
   // The O row and lse of a job come straight from global memory (first touch: a trip to DRAM).
   // They are prefetched into L2 one job ahead (no registers held), so that the loads proper, issued
   // before the wait for the job's tiles, are short.
@@ -348,217 +445,143 @@ __device__ void quad_prepare_role(const QuadParams& p, uint8_t* smem_ptr, uint32
       asm volatile("prefetch.global.L2 [%0];" ::"l"(lse_ptr(n)));
     }
   };
+  // dQ of job n is handled right after the tiles of job n + lag have been prepared: that job's
+  // tiles could only be requested once job n + lag - stages had released its stage, so for
+  // lag = stages - 1 the accumulators of job n complete about when this thread gets there.
+  const int lag = p.n_stages - 1;
   Ring st(p.n_stages);
   prefetch(0);
   prefetch(1);
 #pragma unroll 1
-  for (int n = 0; n < g.count; ++n) {
-    prefetch(n + 2);
-    uint4 o_row[4];
-    float lse = 0.f;
-    if (row_ok) {
-      const uint16_t* orow = row_ptr(n);
+  for (int i = 0; i < g.count + lag; ++i) {
+    const int n = i - lag;       // the job whose dQ is handled in this trip (if >= 0)
+    // the raw q row for the Jacobian of dQ: requested first, used last
+    uint4 raw[4];
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) o_row[ch] = quad_ldg_v4(orow + ch * 8);
-      lse = __ldg(lse_ptr(n));
+    for (int ch = 0; ch < 4; ++ch) raw[ch] = make_uint4(0u, 0u, 0u, 0u);
+    if (n >= 0 && !keeper && row_ok) {
+      const int bw = g.slot + n * p.nslots;
+      const uint16_t* qsrc = static_cast<const uint16_t*>(p.q) + bw * p.q_sbw + g.h * p.q_sh + ig * p.q_sn;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) raw[ch] = quad_ldg_v4(qsrc + ch * 8);
     }
-    const uint32_t base = smem_base + p.off_stage + st.stage * kQStageBytes;
-    if (!qwait(bars + 8u * (qbFull + st.stage), st.phase, ctx, 80)) return;
-    normalise_row<T>(base, lt);              // K^
-    normalise_row<T>(base + 16384u, lt);     // Q^
-    float l2 = INFINITY, dl = 0.f;   // a row past the end of the window: p = exp2(-inf) = 0
-    if (row_ok) {
-      float dlp[4] = {0.f, 0.f, 0.f, 0.f};
+    if (i < g.count) {
+      prefetch(i + 2);
+      uint4 o_row[4];
+      float lse = 0.f;
+      if (row_ok) {
+        const uint16_t* orow = row_ptr(i);
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t wd[4];
-        lds128(base + 24576u + sw64_offset(lt, ch), wd);
-        const uint32_t wo[4] = {o_row[ch].x, o_row[ch].y, o_row[ch].z, o_row[ch].w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          dlp[ch] = fmaf(Elem<T>::lo(wd[i]), Elem<T>::lo(wo[i]), dlp[ch]);
-          dlp[ch] = fmaf(Elem<T>::hi(wd[i]), Elem<T>::hi(wo[i]), dlp[ch]);
-        }
+        for (int ch = 0; ch < 4; ++ch) o_row[ch] = quad_ldg_v4(orow + ch * 8);
+        lse = __ldg(lse_ptr(i));
       }
-      dl = (dlp[0] + dlp[1]) + (dlp[2] + dlp[3]);
-      l2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
+      const uint32_t base = smem_base + p.off_stage + st.stage * kQStageBytes;
+      if (!qwait(bars + 8u * (qbFull + st.stage), st.phase, ctx, 80)) return;
+      normalise_row<T>(base, lt);              // K^
+      normalise_row<T>(base + 16384u, lt);     // Q^
+      float l2 = INFINITY, dl = 0.f;   // a row past the end of the window: p = exp2(-inf) = 0
+      if (row_ok) {
+        float dlp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t wd[4];
+          lds128(base + 24576u + sw64_offset(lt, ch), wd);
+          const uint32_t wo[4] = {o_row[ch].x, o_row[ch].y, o_row[ch].z, o_row[ch].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            dlp[ch] = fmaf(Elem<T>::lo(wd[k]), Elem<T>::lo(wo[k]), dlp[ch]);
+            dlp[ch] = fmaf(Elem<T>::hi(wd[k]), Elem<T>::hi(wo[k]), dlp[ch]);
+          }
+        }
+        dl = (dlp[0] + dlp[1]) + (dlp[2] + dlp[3]);
+        l2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
+      }
+      rowstats[st.stage * 256u + lt] = -l2;            // the compute warpgroups add, never subtract
+      rowstats[st.stage * 256u + 128u + lt] = -dl;
+      fence_proxy_async_smem();
+      mbar_arrive(bars + 8u * (qbReady + st.stage));
+      st.advance();
     }
-    rowstats[st.stage * 256u + lt] = -l2;            // the compute warpgroups add, never subtract
-    rowstats[st.stage * 256u + 128u + lt] = -dl;
-    fence_proxy_async_smem();
-    mbar_arrive(bars + 8u * (qbReady + st.stage));
-    st.advance();
+    if (n >= 0) {
+      const int bw = g.slot + n * p.nslots;
+      rc.par = static_cast<uint32_t>(n) & 1u;
+      // what the partner will push for this job: 64 rows x 128 bytes
+      if (quad && !keeper && rc.row64 == 0u) mbar_arrive_expect_tx(bars + 8u * (qbRecvFull + 2), kQRecvPart);
+      if (!qwait(bars + 8u * qbAccFull, rc.par, ctx, 81)) return;
+      tc_fence_after();
+      uint32_t r[32];
+      tmem_ld32(tmem + lane_base + kQTmDQ, r);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bars + 8u * qbAccFreeQ);
+      if (!quad_row<T>(rc, ctx, r, 2u, quad && keeper, raw, row_ok,
+                       static_cast<uint16_t*>(p.dq) + bw * p.dq_sbw + g.h * p.dq_sh + ig * p.dq_sn, dscale_acc))
+        return;
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------------------
-// The epilogue warpgroup (thread = row), behind the compute warpgroups: once the accumulators of
-// a job are complete, the exchange with the partner CTAs and the epilogues (Jacobian of the L2
-// normalisation, stores, dLogitScale).
-// Row r of an accumulator is tensor-memory lane r.  Of dV and dK (rows = keys of block a; the
-// other term of the sum is held by CTA (a, 1 - b) = rank ^ 1) this CTA keeps the rows of half
-// f = a ^ b and pushes the other half to that partner; of dQ (rows = queries of tile b; partner
-// (1 - a, b) = rank ^ 2) it keeps half 1 - f.  Every thread pushes first and finishes afterwards,
-// so no push ever waits behind a thread that waits for a push.
+// The epilogue warpgroup (thread = row), behind the compute warpgroups: the dV and dK accumulators
+// of every job (pushed to the partner or finished and stored, see quad_row).  Both are read out of
+// tensor memory at once, so that the tensor core can start the next job's sums while the exchange
+// and the epilogues run.
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-__device__ void quad_epilogue_role(const QuadParams& p, uint8_t* smem_ptr, uint32_t smem_base,
-                                 uint32_t bars, uint32_t tmem, const WaitCtx& ctx, uint32_t rank,
-                                 float& dscale_acc) {
+__device__ void quad_epilogue_role(const QuadParams& p, uint32_t smem_base, uint32_t bars, uint32_t tmem,
+                                   const WaitCtx& ctx, uint32_t rank) {
   const QuadGeom g = quad_geom(p, rank);
   if (g.count == 0) return;
   const uint32_t lt = threadIdx.x & 127u;
   const uint32_t lane_base = ((lt >> 5) * 32u) << 16;
-  auto bar = [&](int i) { return bars + 8u * i; };
-  const float scale = load_scale<T>(p.scale, p.scale_is_tensor, g.h);
   const bool quad = p.cluster > 1;
-  const uint32_t half = lt >> 6;
-  const bool keeper = quad ? (half == (g.a ^ g.b)) : true;   // finishes its rows of dV and dK
-  const uint32_t recv_base = smem_base + p.off_recv;
-  const uint32_t row64 = lt & 63u, row_sw = lt & 7u;
-  const int krow = static_cast<int>(g.a * kTileRows + lt), qrow = static_cast<int>(g.b * kTileRows + lt);
-  const bool k_ok = krow < p.N, q_ok = qrow < p.N;
+  const bool keeper = quad ? ((lt >> 6) == (g.a ^ g.b)) : true;   // finishes its rows of dV and dK
+  const int krow = static_cast<int>(g.a * kTileRows + lt);
+  const bool k_ok = krow < p.N;
+  QuadRowCtx rc;
+  rc.bars = bars; rc.recv_base = smem_base + p.off_recv; rc.rank = rank; rc.row64 = lt & 63u; rc.row_sw = lt & 7u;
+  rc.quad = quad; rc.scale = load_scale<T>(p.scale, p.scale_is_tensor, g.h);
+  float unused = 0.f;
 
 #pragma unroll 1
   for (int n = 0; n < g.count; ++n) {
     const int bw = g.slot + n * p.nslots;
-    const uint32_t par = static_cast<uint32_t>(n) & 1u;
-    // the raw k or q row for the Jacobian of this job's epilogue: requested first, used last
-    // (inside a cluster a thread finishes either dV and dK or dQ, so it needs one of the two)
+    rc.par = static_cast<uint32_t>(n) & 1u;
+    // the raw k row for the Jacobian of dK: requested first, used last
     uint4 raw[4];
 #pragma unroll
     for (int ch = 0; ch < 4; ++ch) raw[ch] = make_uint4(0u, 0u, 0u, 0u);
-    const uint16_t* qsrc = static_cast<const uint16_t*>(p.q) + bw * p.q_sbw + g.h * p.q_sh + qrow * p.q_sn;
-    if (keeper) {
-      if (k_ok) {
-        const uint16_t* src = static_cast<const uint16_t*>(p.k) + bw * p.k_sbw + g.h * p.k_sh + krow * p.k_sn;
+    if (keeper && k_ok) {
+      const uint16_t* src = static_cast<const uint16_t*>(p.k) + bw * p.k_sbw + g.h * p.k_sh + krow * p.k_sn;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) raw[ch] = quad_ldg_v4(src + ch * 8);
-      }
-    } else if (q_ok) {
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) raw[ch] = quad_ldg_v4(qsrc + ch * 8);
+      for (int ch = 0; ch < 4; ++ch) raw[ch] = quad_ldg_v4(src + ch * 8);
     }
-    // what the partners will push for this job: 64 rows x 128 bytes per accumulator I finish
-    if (quad && row64 == 0u) {
-      if (keeper) {
-        mbar_arrive_expect_tx(bar(qbRecvFull + 0), kQRecvPart);
-        mbar_arrive_expect_tx(bar(qbRecvFull + 1), kQRecvPart);
-      } else {
-        mbar_arrive_expect_tx(bar(qbRecvFull + 2), kQRecvPart);
-      }
+    // what the partner will push for this job: 64 rows x 128 bytes per accumulator I finish
+    if (quad && keeper && rc.row64 == 0u) {
+      mbar_arrive_expect_tx(bars + 8u * (qbRecvFull + 0), kQRecvPart);
+      mbar_arrive_expect_tx(bars + 8u * (qbRecvFull + 1), kQRecvPart);
     }
-    if (!qwait(bar(qbAccFull), par, ctx, 55)) return;
+    if (!qwait(bars + 8u * qbAccFull, rc.par, ctx, 55)) return;
     tc_fence_after();
     QPROF_BEGIN();
-    // One trip per accumulator (0 dV, 1 dK, 2 dQ), rolled, so that the pushing and the finishing
-    // code exist once (the kernel's roles have to fit the instruction cache together).  dV and dK
-    // are read in the same trip: the tensor core needs both back at the start of the next job (dQ
-    // only at its end).  A keeper pushes dQ and finishes dV and dK; the others push dV and dK and
-    // finish dQ; without a cluster every thread finishes all three.  Every thread pushes before it
-    // finishes, so the pushes a finishing thread waits for never wait for that thread.
-    uint32_t hold[32];
+    uint32_t r[32], hold[32];
+    tmem_ld32(tmem + lane_base + kQTmDV, r);
+    tmem_ld32(tmem + lane_base + kQTmDK, hold);
+    tmem_wait_ld();
+    tc_fence_before();
+    mbar_arrive(bars + 8u * qbAccFree);
+    QPROF_SEG(0);
+    // one trip per accumulator, rolled: the pushing and the finishing code exist once
 #pragma unroll 1
-    for (uint32_t t = 0; t < 3u; ++t) {
-      // a keeper starts with its push (dQ), then dV, dK; everybody else goes 0, 1, 2
-      const uint32_t X = (quad && keeper) ? (t == 0u ? 2u : t - 1u) : t;
-      uint32_t r[32];
-      if (X == 0u) {
-        tmem_ld32(tmem + lane_base + kQTmDV, r);
-        tmem_ld32(tmem + lane_base + kQTmDK, hold);
-      } else if (X == 2u) {
-        tmem_ld32(tmem + lane_base + kQTmDQ, r);
-      }
-      tmem_wait_ld();
-      QPROF_SEG(0);
-      if (X != 1u) {
-        tc_fence_before();
-        mbar_arrive(bar(X == 0u ? qbAccFree : qbAccFreeQ));
-      } else {
+    for (uint32_t X = 0; X < 2u; ++X) {
+      if (X == 1u) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = hold[i];
       }
-      const uint32_t partner = rank ^ (X == 2u ? 2u : 1u);
-      const bool push = quad && (keeper ? X == 2u : X != 2u);
-      if (push) {
-        // the partner has read what I pushed for the previous job; each 16-byte piece credits
-        // the partner's barrier when it has landed there
-        if (!qwait<true>(bar(qbRecvFree + X), par ^ 1u, ctx, 58)) return;
-        const uint32_t dst = cluster_map(recv_base + X * kQRecvPart + row64 * 128u, partner);
-        const uint32_t full = cluster_map(bar(qbRecvFull + X), partner);
-#pragma unroll
-        for (uint32_t ch = 0; ch < 8u; ++ch) st_async_cluster_v4(dst + ((ch ^ row_sw) << 4), &r[4 * ch], full);
-        QPROF_SEG(1);
-        continue;
-      }
-      if (quad) {
-        if (!qwait<true>(bar(qbRecvFull + X), par, ctx, 59)) return;
-        QPROF_SEG(2);
-        const uint32_t src = recv_base + X * kQRecvPart + row64 * 128u;
-#pragma unroll
-        for (uint32_t ch = 0; ch < 8u; ++ch) {
-          uint32_t w4[4];
-          lds128(src + ((ch ^ row_sw) << 4), w4);
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            r[4 * ch + i] = __float_as_uint(__uint_as_float(r[4 * ch + i]) + __uint_as_float(w4[i]));
-        }
-        // (the additions above have consumed every loaded value: the buffer may be overwritten)
-        mbar_arrive_cluster_relaxed(cluster_map(bar(qbRecvFree + X), partner));
-        QPROF_SEG(3);
-      }
-      const bool ok = X == 2u ? q_ok : k_ok;
-      if (X == 2u && keeper) {
-        // without a cluster this thread finishes all three: the q row is fetched only now
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) raw[ch] = q_ok ? quad_ldg_v4(qsrc + ch * 8) : make_uint4(0u, 0u, 0u, 0u);
-      }
-      // rows of dV are stored as they are; rows of dK^ / dQ^ go through the Jacobian of the
-      // L2 normalisation: dx = scale (dX' - x^ (x^ . dX')) / |x| from the raw row x
-      float fmul = 1.f, cq = 0.f;
-      if (X != 0u) {
-        float ss = 0.f, qd = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint32_t w4[4] = {raw[ch].x, raw[ch].y, raw[ch].z, raw[ch].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float x0 = Elem<T>::lo(w4[e]), x1 = Elem<T>::hi(w4[e]);
-            ss = fmaf(x0, x0, ss);
-            ss = fmaf(x1, x1, ss);
-            qd = fmaf(x0, __uint_as_float(r[8 * ch + 2 * e]), qd);
-            qd = fmaf(x1, __uint_as_float(r[8 * ch + 2 * e + 1]), qd);
-          }
-        }
-        const float rn = rsqrtf(fmaxf(ss, 1e-24f));
-        const float dot = qd * rn;
-        if (X == 2u && ok) dscale_acc += dot;
-        fmul = scale * rn;
-        cq = rn * dot;
-      }
-      QPROF_SEG(4);
-      if (ok) {
-        uint16_t* dst;
-        if (X == 0u) dst = static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + krow * p.dv_sn;
-        else if (X == 1u) dst = static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + krow * p.dk_sn;
-        else dst = static_cast<uint16_t*>(p.dq) + bw * p.dq_sbw + g.h * p.dq_sh + qrow * p.dq_sn;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint32_t w4[4] = {raw[ch].x, raw[ch].y, raw[ch].z, raw[ch].w};
-          uint32_t o4[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float v0 = __uint_as_float(r[8 * ch + 2 * e]), v1 = __uint_as_float(r[8 * ch + 2 * e + 1]);
-            if (X != 0u) {
-              v0 = fmul * (v0 - Elem<T>::lo(w4[e]) * cq);
-              v1 = fmul * (v1 - Elem<T>::hi(w4[e]) * cq);
-            }
-            o4[e] = Elem<T>::pack(v0, v1);
-          }
-          *reinterpret_cast<uint4*>(dst + 8 * ch) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
-        }
-      }
-      QPROF_SEG(5);
+      uint16_t* dst = X == 0u ? static_cast<uint16_t*>(p.dv) + bw * p.dv_sbw + g.h * p.dv_sh + krow * p.dv_sn
+                              : static_cast<uint16_t*>(p.dk) + bw * p.dk_sbw + g.h * p.dk_sh + krow * p.dk_sn;
+      if (!quad_row<T>(rc, ctx, r, X, quad && !keeper, raw, k_ok, dst, unused)) return;
+      QPROF_SEG(1 + X);
     }
   }
 }
@@ -776,7 +799,7 @@ __global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_
       if (i >= qbReady && i < qbFree) count = 128u;            // the preparing warpgroup
       else if (i >= qbMaskFree && i < qbBiasFull) count = 256u;
       else if (i >= qbPReady && i < qbAccFull) count = 128u;
-      else if (i == qbAccFree || i == qbAccFreeQ) count = 128u; // the epilogue warpgroup
+      else if (i == qbAccFree || i == qbAccFreeQ) count = 128u; // the epilogue / preparing warpgroup
       else if (i >= qbRecvFull && i < qbRecvFree) count = 1u;  // one arrive.expect_tx; the data credits the rest
       else if (i >= qbRecvFree && i < qbDsFree) count = 64u;
       mbar_init(bars + 8u * i, count);
@@ -822,18 +845,21 @@ __global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_
   // 640 threads start with 96 registers each.  setmaxnreg only moves registers inside what the
   // CTA was given at launch (an increase beyond it would wait for ever), so the four budgets
   // below must not add up to more than 640 x 96.
-  constexpr uint32_t kRegCompute = 128, kRegEpilogue = 128, kRegPrepare = 56, kRegIssue = 40;
+  constexpr uint32_t kRegCompute = 112, kRegEpilogue = 112, kRegPrepare = 104, kRegIssue = 40;
   static_assert(2 * 128 * kRegCompute + 128 * (kRegEpilogue + kRegPrepare + kRegIssue) <= kQuadThreads * 96,
                 "register budgets exceed the launch allocation");
+  // (setmaxnreg.inc below what a thread already has, or .dec above it, is an illegal instruction)
+  static_assert(kRegCompute >= 96 && kRegEpilogue >= 96 && kRegPrepare >= 96 && kRegIssue <= 96,
+                "increase / decrease directions do not match the launch allocation of 96");
   if (warp < 8) {
     reg_alloc<kRegCompute>();
     quad_compute_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, rank);
   } else if (warp < 12) {
     reg_alloc<kRegEpilogue>();
-    quad_epilogue_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, rank, dscale_acc);
+    quad_epilogue_role<T>(p, smem_base, bars, tmem, ctx, rank);
   } else if (warp < 16) {
-    reg_dealloc<kRegPrepare>();
-    quad_prepare_role<T>(p, smem_raw, smem_base, bars, ctx, rank);
+    reg_alloc<kRegPrepare>();
+    quad_prepare_role<T>(p, smem_raw, smem_base, bars, tmem, ctx, rank, dscale_acc);
   } else {
     reg_dealloc<kRegIssue>();
     if (lane == 0) {
@@ -843,10 +869,10 @@ __global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_
   }
   __syncwarp();
   // deterministic CTA-wide sum of the dLogitScale contributions
-  if (warp >= 8 && warp < 12) {
+  if (warp >= 12 && warp < 16) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) dscale_acc += __shfl_xor_sync(0xFFFFFFFFu, dscale_acc, off);
-    if (lane == 0) warp_sums[warp - 8] = dscale_acc;
+    if (lane == 0) warp_sums[warp - 12] = dscale_acc;
   }
   tc_fence_before();
   __syncthreads();

@@ -277,10 +277,12 @@ def sharded_parity_check(w, device, reducer: Optional[PeerReducer] = None, image
                               reducer=reducer)
     so, sdq, sdk, sdv, sds, sdb = step.replay()
     torch.cuda.synchronize(device)
-    exact = all(torch.equal(a, b[sl]) for a, b in zip((so, sdq, sdk, sdv), ref[:4]))
     rel = lambda a, b: float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30))
+    # worst absolute deviation of this rank's o / dq / dk / dv from the unsharded run (0 = bitwise equal)
+    worst = [float((a.float() - b[sl].float()).abs().max()) for a, b in zip((so, sdq, sdk, sdv), ref[:4])]
+    exact = all(torch.equal(a, b[sl]) for a, b in zip((so, sdq, sdk, sdv), ref[:4]))
     dev_db, dev_ds = rel(sdb, ref[5]), rel(sds, ref[4])
-    stats = torch.tensor([0.0 if exact else 1.0, dev_db, dev_ds], device=device)
+    stats = torch.tensor([0.0 if exact else 1.0, dev_db, dev_ds] + worst, device=device)
     dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     # every rank must also hold the SAME summed gradients, bit for bit
     mine = torch.cat([sdb.float().reshape(-1), sds.float().reshape(-1)])
@@ -288,6 +290,7 @@ def sharded_parity_check(w, device, reducer: Optional[PeerReducer] = None, image
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     return dict(images=small.batch, window_results_bitwise_equal=bool(stats[0].item() == 0.0),
+                max_abs_dev_o_dq_dk_dv=[float(x) for x in stats[3:7]],
                 dbias_rel_dev=float(stats[1]), dscale_rel_dev=float(stats[2]),
                 sums_identical_on_all_ranks=bool(torch.equal(lo, hi)))
 
