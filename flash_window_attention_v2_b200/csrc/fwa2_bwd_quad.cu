@@ -344,14 +344,19 @@ __device__ __forceinline__ bool quad_row(const QuadRowCtx& c, const WaitCtx& ctx
   if (push) {
     // the partner has read what I pushed for the previous job; each 16-byte piece credits the
     // partner's barrier when it has landed there
-    if (!qwait<true>(free_, c.par ^ 1u, ctx, 58)) return false;
+    // (a plain wait: the partner's arrival carries no data, it only says "read")
+    if (!qwait(free_, c.par ^ 1u, ctx, 58)) return false;
     const uint32_t dst_row = cluster_map(slot, partner), dst_bar = cluster_map(full, partner);
 #pragma unroll
     for (uint32_t ch = 0; ch < 8u; ++ch) st_async_cluster_v4(dst_row + ((ch ^ c.row_sw) << 4), &r[4 * ch], dst_bar);
     return true;
   }
   if (c.quad) {
-    if (!qwait<true>(full, c.par, ctx, 59)) return false;
+    // The rows were delivered by st.async, which completes on this barrier with transaction
+    // bytes like a TMA load: observing the phase makes them visible, so a plain wait is enough.
+    // (An acquire at cluster scope would also wait for every global load this thread still has in
+    // flight -- the raw row requested at the top of the job -- which cost thousands of cycles.)
+    if (!qwait(full, c.par, ctx, 59)) return false;
 #pragma unroll
     for (uint32_t ch = 0; ch < 8u; ++ch) {
       uint32_t w4[4];
