@@ -2,10 +2,9 @@
 //
 // Some hosts of this library cannot hand it a workspace: a plugin running inside a framework that
 // owns the only allocator, a steady-state serving loop that forbids allocator traffic after
-// warm-up, code that runs between cudaStreamBeginCapture and cudaStreamEndCapture (where
-// cudaMalloc is illegal).  For them the scratch the backward needs lives in a fixed array in the
-// library's own device image: it exists on every GPU that loads the library, from load until
-// exit, whether or not this entry point is ever used.
+// warm-up, code in a context where cudaMalloc is not allowed.  For them the scratch the backward
+// needs lives in a fixed array in the library's own device image: it exists on every GPU that
+// loads the library, from load until exit, whether or not this entry point is ever used.
 #include "../../include/fwa2.h"
 
 #include <cuda_runtime.h>

@@ -179,9 +179,9 @@ int fwa2_cpb_bias_backward(const float* dbias_f32, const void* table, int32_t ta
 /* Backward pass that allocates nothing and takes no workspace.  (No counterpart in the reference
  * project, which allocates its fp32 accumulators with torch on every call.)
  *
- * For callers that cannot provide scratch memory: code between cudaStreamBeginCapture and
- * cudaStreamEndCapture, where cudaMalloc is not allowed; a plugin inside a framework that keeps
- * the device allocator to itself; a serving loop that bans allocator calls once it is warm.
+ * For callers that cannot provide scratch memory: a plugin inside a framework that keeps the
+ * device allocator to itself; a serving loop that bans allocator calls once it is warm; code in a
+ * context where cudaMalloc is not allowed.
  * Same arguments and results as fwa2_backward, except that `workspace` / `workspace_bytes` are
  * ignored: the scratch is a fixed array of FWA2_STATIC_SCRATCH_BYTES inside the library's
  * device image, present on every GPU that loads the library until the process exits.

@@ -1,7 +1,7 @@
 """The allocation-free backward entry point (fwa2_backward_static_scratch).
 
-It serves callers that may not allocate device memory at the point of the call (inside a stream
-capture, inside a host framework that owns the allocator, in a warmed-up serving loop).  The test
+It serves callers that may not allocate device memory at the point of the call (inside a host
+framework that owns the allocator, in a warmed-up serving loop that bans allocator calls).  The test
 goes through the C ABI directly: everything the call touches is allocated beforehand, the entry
 point gets no workspace, and its results must equal those of the regular entry point (the
 kernels are deterministic, so the comparison is exact) on two calls in a row, the second of
