@@ -450,3 +450,36 @@ def test_random_shapes(w, kw, dev):
     precision, not of the kernels (measured over six seeds; the outputs o and dv stay at 0.2 %)."""
     got, ref, ins = run_case(w, dev, **kw)
     check(w, got, ref, ins)
+
+
+def test_peer_reduce_kernel_single_process(dev):
+    """The fused cross-GPU sum + cast kernel, exercised on ONE GPU: the buffers of three "ranks" live
+    in this process and their flags are set beforehand, so the kernel finds every peer ready and
+    never waits (kernels that wait for one another must not share a GPU).  Its result must equal
+    summing the buffers in rank order with torch and casting with fwa2_finalize_grads, bit for bit."""
+    import ctypes as C
+    from flash_window_attention_v2_b200 import _lib
+    from flash_window_attention_v2_b200 import kernels as K
+    L = _lib.lib()
+    h, n, world, epoch = 3, 144, 3, 5
+    g = torch.Generator(device="cpu").manual_seed(7)
+    parts = [torch.randn(h * n * n + h, generator=g).to(dev) for _ in range(world)]
+    flags = [torch.full((8,), epoch, dtype=torch.int32, device=dev) for _ in range(world)]
+    ls = torch.tensor([1.0, 5.0, 2.0], device=dev).to(torch.bfloat16).reshape(h, 1, 1)   # head 1 is clamped
+    total = parts[0] + parts[1]
+    total = total + parts[2]                         # ascending rank order, like the kernel
+    db_ref = torch.empty(h, n, n, dtype=torch.bfloat16, device=dev)
+    ds_ref = torch.empty(h, 1, 1, dtype=torch.bfloat16, device=dev)
+    K.finalize_grads(total.contiguous(), ls, db_ref, ds_ref)
+    for rank in range(world):
+        db = torch.zeros_like(db_ref)
+        ds = torch.zeros_like(ds_ref)
+        pp = (C.c_void_p * world)(*[p.data_ptr() for p in parts])
+        ff = (C.c_void_p * world)(*[f.data_ptr() for f in flags])
+        rc = L.fwa2_peer_reduce_finalize(pp, ff, rank, world, epoch, _lib.FWA2_BF16, h, n, ls.data_ptr(),
+                                         db.data_ptr(), ds.data_ptr(), K._status(dev).data_ptr(),
+                                         C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        assert rc == 0
+        K.check_device_status(dev)
+        assert torch.equal(db, db_ref) and torch.equal(ds, ds_ref), rank
+        assert float(ds[1]) == 0.0            # g = 5 > ln 100: gated
