@@ -13,7 +13,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libfwa2_b200.so")
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["fwa2_api.cu", "fwa2_fwd.cu", "fwa2_bwd.cu", "fwa2_bwd_quad.cu", "fwa2_reduce.cu", "fwa2_selftest.cu",
+SOURCES = ["fwa2_api.cu", "fwa2_fwd.cu", "fwa2_fwd_duo.cu", "fwa2_bwd.cu", "fwa2_bwd_quad.cu", "fwa2_reduce.cu", "fwa2_selftest.cu",
            "fwa2_static_scratch.cu", "fwa2_cpb_bias.cu", "fwa2_peer_reduce.cu"]
 
 FWA2_ABI_VERSION = 1

@@ -13,6 +13,7 @@ namespace fwa2 {
 
 cudaError_t launch_fwd(const FwdParams& p, int dtype_is_bf16, int p_in_tmem, int grid,
                        cudaStream_t stream);
+cudaError_t launch_fwd_duo(const FwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
 cudaError_t launch_bwd(const BwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
 cudaError_t launch_bwd_quad(const QuadParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
 int quad_max_active_clusters(int dtype_is_bf16, int cluster, uint32_t smem_bytes);
@@ -298,8 +299,43 @@ extern "C" int fwa2_forward(const fwa2_fwd_args* a, void* stream) {
   p.trace.buf = reinterpret_cast<unsigned long long*>(a->developer0);
   p.trace.cap = a->developer0 != nullptr ? a->developer1 : 0;
 
-  // ---- shared memory layout: prefer two CTAs per SM ----
   const bool p_in_tmem = (a->variant & FWA2_FWD_P_IN_SMEM) == 0;
+  const uint32_t budget_two = static_cast<uint32_t>(dev.max_smem_optin + 1024) / 2u - 1024u;
+
+  // ---- windows of 129 to 256 tokens: two softmax warpgroups per CTA, one per tile of the unit ----
+  if (a->n > 128 && a->n <= 256 && p_in_tmem && (a->variant & FWA2_FWD_GENERAL_KERNEL) == 0) {
+    const uint32_t rows = static_cast<uint32_t>((a->n + 63) / 64) * 64u;
+    p.kv_stage_bytes = rows * kRowBytes;
+    // K and Q have one buffer each.  Four table stages (two per tile) matter more than a second
+    // V buffer: the next unit's V is not needed before its first step is through the softmax.
+    const bool tables = has_bias || has_mask;
+    const uint32_t fixed = rows * kRowBytes + 4u * kBoxBytes + kCtrlBytes;
+    const uint32_t t_stage = 2u * kTableTileBytes;
+    uint32_t nv = 2, nt = tables ? 4u : 0u;
+    if (fixed + nv * rows * kRowBytes + nt * t_stage > budget_two) nv = 1;
+    if (fixed + nv * rows * kRowBytes + nt * t_stage > budget_two) nt = 3;
+    p.n_kv_stages = static_cast<int>(nv);               // of V
+    p.n_bm_stages = static_cast<int>(tables ? nt : 3u);
+    p.off_kv = 0;                                       // K
+    p.off_q = p.off_kv + rows * kRowBytes;              // Q: 256 rows
+    p.off_p = p.off_q + 4u * kBoxBytes;                 // V
+    p.off_bm = p.off_p + nv * rows * kRowBytes;         // table chunks: stages of [bias | mask]
+    p.off_ctrl = p.off_bm + nt * t_stage;
+    p.smem_bytes = p.off_ctrl + kCtrlBytes;
+    if (p.smem_bytes <= budget_two) {
+      int grid = dev.sm_count * 2;
+      if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
+      if (grid > p.n_jobs) grid = p.n_jobs;
+      const cudaError_t e = launch_fwd_duo(p, a->dtype == FWA2_BF16, grid, static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) {
+        g_last_cuda_error = static_cast<int>(e);
+        return FWA2_ERR_LAUNCH;
+      }
+      return FWA2_OK;
+    }
+  }
+
+  // ---- shared memory layout: prefer two CTAs per SM ----
   const uint32_t rows_kv = p.pair_mode ? 128u : static_cast<uint32_t>((a->n + 63) / 64) * 64u;
   p.kv_stage_bytes = 2u * rows_kv * kRowBytes;
   const uint32_t p_bytes = p_in_tmem ? 0u : (p.pair_mode ? 32768u : 16384u);
@@ -307,7 +343,6 @@ extern "C" int fwa2_forward(const fwa2_fwd_args* a, void* stream) {
   auto total = [&](uint32_t nkv, uint32_t nbm) {
     return nkv * p.kv_stage_bytes + 2u * 2u * kBoxBytes + nbm * bm_stage + p_bytes + kCtrlBytes;
   };
-  const uint32_t budget_two = static_cast<uint32_t>(dev.max_smem_optin + 1024) / 2u - 1024u;
   const uint32_t budget_one = static_cast<uint32_t>(dev.max_smem_optin);
   uint32_t nkv = 2, nbm = 3;
   int ctas_per_sm = 2;

@@ -55,6 +55,9 @@ enum fwa2_error {
 #define FWA2_BWD_GENERAL_KERNEL 16 /* backward: windows of 65 to 256 tokens normally run on the
                                     cluster kernel (one 128 x 128 score tile per CTA); this bit
                                     selects the general kernel for them instead */
+#define FWA2_FWD_GENERAL_KERNEL 32 /* forward: windows of 129 to 256 tokens normally run on the
+                                    kernel with two softmax warpgroups per CTA (one per 128-row
+                                    tile of the unit); this bit selects the general kernel */
 
 /* A (BW, H, N, 32) tensor of 16-bit elements with unit stride along the last axis.
  * Strides are in elements. */

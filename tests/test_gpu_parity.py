@@ -251,6 +251,41 @@ def test_both_backward_kernels_for_mid_size_windows(variant, dev):
                             mask=t["mask"]))
 
 
+@pytest.mark.parametrize("variant", [0, 32], ids=["two_warpgroup_kernel", "general_kernel"])
+@pytest.mark.parametrize("window,dtype,kw", [
+    (16, "bf16", {}), (16, "fp16", {}), (12, "bf16", {}), (14, "fp16", {}), (13, "bf16", {}),
+    (16, "bf16", dict(with_mask=False)), (16, "fp16", dict(with_bias=False)),
+    (16, "bf16", dict(with_mask=False, with_bias=False)), (16, "bf16", dict(with_scale=False)),
+], ids=["n256_bf16", "n256_fp16", "n144", "n196_fp16", "n169", "n256_nomask", "n256_nobias", "n256_plain",
+        "n256_noscale"])
+def test_both_forward_kernels_for_windows_of_129_to_256_tokens(window, dtype, kw, variant, dev):
+    """Windows of 129 to 256 tokens have two forward kernels (two softmax warpgroups per CTA is the
+    default, the general one is selected by a variant bit): o and lse of both are held to the
+    oracle, with and without each table, on more units than one pass of the grid covers."""
+    w = Workload(f"w{window}", batch=7, nw=16, heads=3, window=window, dtype=dtype)
+    got, ref, ins = run_case(w, dev, via="boundary", variant=variant, **kw)
+    check(w, got, ref, ins)
+
+
+def test_forward_rows_without_any_admissible_key(dev):
+    """The reference's own benchmark inputs (masks of 0 / -inf drawn at random, N(0, 1) logit scale):
+    both forward kernels agree on which rows have lse = -inf and on everything else."""
+    from flash_window_attention_v2_b200 import kernels as K
+    from flash_window_attention_v2_b200.workloads import make_reference_recipe_inputs
+    w = Workload("recipe", batch=2, nw=4, heads=3, window=16, dtype="fp16")
+    t = make_reference_recipe_inputs(w, seed=3, device=dev)
+    t["mask"][1, 5, :] = float("-inf")          # one row with no admissible key at all
+    res = [K._flash_attn_forward(t["q"], t["k"], t["v"], t["logit_scale"], bias=t["bias"], mask=t["mask"],
+                                 scale_type="tensor", _variant=v) for v in (0, 32)]
+    K.check_device_status(dev)
+    (o1, l1, _), (o0, l0, _) = res
+    fin = torch.isfinite(l0[..., : w.n])
+    assert bool((torch.isfinite(l1[..., : w.n]) == fin).all()) and not bool(fin.all())
+    assert float((l1[..., : w.n][fin] - l0[..., : w.n][fin]).abs().max()) < 1e-3
+    assert bool(torch.isfinite(o1).all())
+    assert float((o1.float() - o0.float()).norm() / o0.float().norm()) < 2e-3
+
+
 @pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg4"])
 def test_full_size_backward_against_the_classic_path(name, dev):
     """The benchmark configurations at FULL size, forward and backward: dq, dk, dv of a sample of
