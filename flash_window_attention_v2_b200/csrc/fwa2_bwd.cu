@@ -515,6 +515,9 @@ __device__ void bwd_compute_role(const BwdParams& p, uint8_t* smem_ptr, uint32_t
           }
           trace_ev(tr, 7);
           if (any_table) {
+            // (behind the wait for the stores of the values computed from the table words: by then
+            // the shared-memory loads of every one of them have certainly completed)
+            tmem_wait_st();
             mbar_arrive(bar(kbBmFree + 2 * wg + st));
             bm_ring.advance();
           }

@@ -260,11 +260,13 @@ __device__ void quad_compute_role(const QuadParams& p, uint8_t* smem_ptr, uint32
       }
     }
     QPROF_SEG(10);
+    tmem_wait_st();
+    // (the mask stage is handed back behind the wait for the stores of the values computed from
+    // its words: by then the shared-memory loads of every one of them have certainly completed)
     if (p.has_mask) {
       mbar_arrive(bar(qbMaskFree + mk.stage));
       mk.advance();
     }
-    tmem_wait_st();
     QPROF_SEG(11);
     // dS also goes to shared memory (A operand of dQ^ += dS K^), but only now: the product that
     // read the previous job's copy was issued while this step was being computed, so it is

@@ -78,6 +78,7 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
   const uint32_t hf = tid >> 6;
   const uint32_t lane_base = ((tid >> 5) * 32u) << 16;
   const bool any_table = p.has_bias || p.has_mask;
+  const uint32_t rt_zero = static_cast<uint32_t>(p.N) >> 30;   // 0, but not to the compiler
   auto bar = [&](int i) { return bars + 8u * i; };
 
   if (sh.pair) {
@@ -321,11 +322,13 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
               const uint32_t st = bm_ring.stage;
               const uint32_t bm_base = smem_base + p.off_bm + st * (2u * kTableTileBytes);
               if (!mbar_wait(bar(kBarBmFull + st), bm_ring.phase, ctx, 13)) return;
+              uint32_t loaded = 0u;
 #pragma unroll
               for (int ch = 0; ch < 4; ++ch) {
                 uint32_t wb[4] = {0u, 0u, 0u, 0u}, wm[4] = {0u, 0u, 0u, 0u};
                 if (p.has_bias) lds128(bm_base + sw64_offset(tid, ch), wb);
                 if (p.has_mask) lds128(bm_base + kTableTileBytes + sw64_offset(tid, ch), wm);
+                loaded |= wb[0] | wm[0];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const int j = c2 * 32 + ch * 8 + i * 2;
@@ -333,7 +336,7 @@ __device__ void fwd_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_
                   x[j + 1] = fmaf(x[j + 1], scale, Elem<T>::hi(wb[i])) + Elem<T>::hi(wm[i]);
                 }
               }
-              mbar_arrive(bar(kBarBmFree + st));
+              mbar_arrive_after_loads(bar(kBarBmFree + st), loaded, rt_zero);
               bm_ring.advance();
             } else {
 #pragma unroll

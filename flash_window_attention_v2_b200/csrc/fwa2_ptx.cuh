@@ -40,6 +40,17 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrival that hands a shared-memory buffer back to an asynchronous producer (TMA) after this
+// thread has read it with ld.shared.  A plain arrival may be issued while those loads are still
+// outstanding: only the arithmetic on the loaded values is tied to them, and arithmetic may be
+// scheduled after an arrival that does not depend on it -- the producer has then been seen to
+// overwrite the buffer under a warp that had not got its data yet.  Here the barrier address is
+// made to depend on the loaded words (`loaded`: an OR over one word of every load; `zero`: a value
+// that is 0 at run time but unknown to the compiler), so the arrival cannot issue before they are
+// all in registers.
+__device__ __forceinline__ void mbar_arrive_after_loads(uint32_t bar, uint32_t loaded, uint32_t zero) {
+  mbar_arrive(bar + (loaded & zero));
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
