@@ -233,23 +233,25 @@ __device__ void quad_compute_role(const QuadParams& p, uint8_t* smem_ptr, uint32
       const float* nl2 = rowstats + st.stage * 256u + wg * 64u;
       const float* nd = rowstats + st.stage * 256u + 128u + wg * 64u;
       const uint32_t mask_row = smem_base + p.off_mask + mk.stage * kQTableBytes + tab_row;
-      // Two trips of 32 queries (one table chunk each), each written out as two pieces of
-      // sixteen.  The trip is rolled to keep the code small (all roles of the kernel have to fit
-      // the instruction cache together); its sixteen bias words are picked out of the 32 the
-      // thread holds with one select each.
+      // Two trips of 32 queries (one table chunk each), each of two pieces of sixteen.  Both
+      // loops are rolled to keep the code small (all roles of the kernel have to fit the
+      // instruction cache together): the code of a piece exists once, and its eight bias words
+      // are picked out of the 32 the thread holds with selects.
 #pragma unroll 1
       for (uint32_t c = 0; c < 2u; ++c) {
         uint32_t wsel[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) wsel[i] = c == 0u ? wb[i] : wb[16 + i];
         const uint32_t mchunk = mask_row + (2u * wg + c) * static_cast<uint32_t>(kTableTileBytes);
-#pragma unroll
+#pragma unroll 1
         for (uint32_t hh = 0; hh < 2u; ++hh) {
-          uint32_t sv[16], dv[16], pw[8], dw[8];
+          uint32_t sv[16], dv[16], pw[8], dw[8], w8[8];
           tmem_ld16(tm_s + 32u * c + 16u * hh, sv);
           tmem_ld16(tm_d + 32u * c + 16u * hh, dv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w8[i] = hh == 0u ? wsel[i] : wsel[8 + i];
           tmem_wait_ld();
-          quad_half<T>(sv, dv, &wsel[8 * hh], p.has_mask != 0, mchunk + (((2u * hh) ^ tab_sw) << 4),
+          quad_half<T>(sv, dv, w8, p.has_mask != 0, mchunk + (((2u * hh) ^ tab_sw) << 4),
                        mchunk + (((2u * hh + 1u) ^ tab_sw) << 4), nl2 + 32u * c + 16u * hh, nd + 32u * c + 16u * hh,
                        scale, pw, dw);
           // P^T and dS^T go back over the first 16 columns of this chunk's own S^T / dP^T
@@ -593,8 +595,8 @@ __device__ void quad_epilogue_role(const QuadParams& p, uint32_t smem_base, uint
   }
 }
 
-// The issuing thread is the busiest in the CTA (some forty products per job), so a job is written
-// out as straight-line code: tensor-memory addresses and descriptor offsets are constants, and a
+// The issuing thread (some forty to fifty-six products per job).  Descriptors are assembled from
+// a template with one addition: tensor-memory addresses and descriptor offsets are cheap, and a
 // descriptor costs one addition (the stage's base address, in 16-byte units, plus a constant).
 struct Desc16 {
   uint32_t lo, hi;   // descriptor for shared-memory address 0; add (address >> 4) to lo
@@ -626,111 +628,75 @@ __device__ void quad_mma_role(const QuadParams& p, uint32_t smem_base, uint32_t 
   const bool with_db = p.db_partial != nullptr;
   const uint32_t ident16_c = smem16(smem_base + p.off_ident);
   const uint32_t ds16_c = smem16(smem_base + p.off_ds);
-  // Per-job copies that the compiler must treat as fresh values: otherwise it computes the some
-  // forty (base + constant) addresses of a job once, outside the loop, and keeps them all in
-  // registers that this thread does not have.
-  uint32_t tm = tmem, ident16 = ident16_c, ds16 = ds16_c;
-  auto refresh = [&]() {
-    tm = tmem;
-    ident16 = ident16_c;
-    ds16 = ds16_c;
-    asm volatile("" : "+r"(tm), "+r"(ident16), "+r"(ds16));
-  };
   constexpr uint32_t kK = 0u, kV = 8192u, kQ = 16384u, kDO = 24576u;   // byte offsets inside a stage
 
-  // S^T = K^ Q^^T and dP^T = V dO^T for the 64 queries of step W (a compile-time constant)
-  auto issue_sdp = [&](auto W, uint32_t s16) {
-    constexpr uint32_t w = decltype(W)::value;
-    constexpr uint32_t row_off = w * (kStepCols * kRowBytes);
-#pragma unroll
-    for (uint32_t k = 0; k < 2u; ++k) {
-      mma_ss(tm + w * 128u + kQTmS, desc16_at(dk64, s16, kK + 32u * k), desc16_at(dk64, s16, kQ + row_off + 32u * k),
-             idesc_s, k);
-      mma_ss(tm + w * 128u + kQTmDP, desc16_at(dk64, s16, kV + 32u * k),
-             desc16_at(dk64, s16, kDO + row_off + 32u * k), idesc_s, k);
-    }
-    mma_commit(bar(qbSFull + static_cast<int>(w)));
-  };
-  // dV += P^T dO, dK^ += dS^T Q^, dB^T += dS^T I for step W (each step has its own copy of the
-  // identity tile)
-  auto issue_acc = [&](auto W, uint32_t s16) {
-    constexpr uint32_t w = decltype(W)::value;
-#pragma unroll
-    for (uint32_t c = 0; c < 2u; ++c) {
-#pragma unroll
-      for (uint32_t k = 0; k < 2u; ++k) {
-        const uint32_t row_off = (w * kStepCols + c * kChunkCols) * kRowBytes + k * 1024u;
-        const uint32_t a_p = tm + w * 128u + kQTmS + 32u * c + 8u * k;
-        const uint32_t a_ds = tm + w * 128u + kQTmDP + 32u * c + 8u * k;
-        const uint32_t acc = (w | c | k) ? 1u : 0u;
-        mma_ts(tm + kQTmDV, a_p, desc16_at(dm64, s16, kDO + row_off), idesc_acc, acc);
-        mma_ts(tm + kQTmDK, a_ds, desc16_at(dm64, s16, kQ + row_off), idesc_acc, acc);
-        if (with_db)
-          mma_ts(tm + kQTmDB + 64u * w + 32u * c, a_ds, desc16_at(dm64, ident16, 2048u * w + k * 1024u), idesc_acc, 1u);
-      }
-    }
-  };
-  using W0 = std::integral_constant<uint32_t, 0u>;
-  using W1 = std::integral_constant<uint32_t, 1u>;
-
-  Ring st(p.n_stages);
-  if (!qwait(bar(qbReady + 0), 0u, ctx, 60)) return;
-  tc_fence_after();
-  {
-    // the first job's scores (runs once: a small rolled loop instead of two more copies)
-    const uint32_t s16 = smem16(smem_base + p.off_stage);
+  // Everything is issued from rolled loops with one call site each: this role's code has to share
+  // the instruction cache with four other roles, and the issuing thread has time to spare.
+  Ring st(p.n_stages);            // the stage of job n + 1 (trip n = -1 issues the first job's scores)
+  uint32_t s16 = 0u;              // the stage of job n, in 16-byte units
+#pragma unroll 1
+  for (int n = -1; n < g.count; ++n) {
+    const uint32_t par = static_cast<uint32_t>(n) & 1u;
+    const bool has_next = n + 1 < g.count;
+    const uint32_t n16 = smem16(smem_base + p.off_stage + st.stage * kQStageBytes);
 #pragma unroll 1
     for (uint32_t w = 0; w < 2u; ++w) {
-      const uint32_t row_off = w * (kStepCols * kRowBytes);
+      const uint32_t tw = tmem + w * 128u;
+      if (n >= 0) {
+        // the accumulators of the previous job have been read out
+        if (w == 0u && n > 0) {
+          if (!qwait(bar(qbAccFree), par ^ 1u, ctx, 62)) return;
+        }
+        if (!qwait(bar(qbPReady + static_cast<int>(w)), par, ctx, 64)) return;
+        tc_fence_after();
+        // dV += P^T dO, dK^ += dS^T Q^, dB^T += dS^T I for step w (each step has its own copy of
+        // the identity tile)
 #pragma unroll 1
-      for (uint32_t k = 0; k < 2u; ++k) {
-        mma_ss(tmem + w * 128u + kQTmS, desc16_at(dk64, s16, kK + 32u * k), desc16_at(dk64, s16, kQ + row_off + 32u * k),
-               idesc_s, k);
-        mma_ss(tmem + w * 128u + kQTmDP, desc16_at(dk64, s16, kV + 32u * k),
-               desc16_at(dk64, s16, kDO + row_off + 32u * k), idesc_s, k);
+        for (uint32_t ck = 0; ck < 4u; ++ck) {
+          const uint32_t c = ck >> 1, k = ck & 1u;
+          const uint32_t row_off = (w * kStepCols + c * kChunkCols) * kRowBytes + k * 1024u;
+          const uint32_t a_p = tw + kQTmS + 32u * c + 8u * k, a_ds = tw + kQTmDP + 32u * c + 8u * k;
+          const uint32_t acc = (w | ck) ? 1u : 0u;
+          mma_ts(tmem + kQTmDV, a_p, desc16_at(dm64, s16, kDO + row_off), idesc_acc, acc);
+          mma_ts(tmem + kQTmDK, a_ds, desc16_at(dm64, s16, kQ + row_off), idesc_acc, acc);
+          if (with_db)
+            mma_ts(tmem + kQTmDB + 64u * w + 32u * c, a_ds, desc16_at(dm64, ident16_c, 2048u * w + k * 1024u),
+                   idesc_acc, 1u);
+        }
       }
-      mma_commit(bar(qbSFull + static_cast<int>(w)));
-    }
-  }
-
+      // The next job's scores of step w go over this job's P^T / dS^T of the step (the tensor core
+      // works in issue order), so that the warpgroup can go on while the rest is issued:
+      // S^T = K^ Q^^T and dP^T = V dO^T for the 64 queries of the step.
+      if (has_next) {
+        if (w == 0u) {
+          if (!qwait(bar(qbReady + st.stage), st.phase, ctx, 66)) return;
+          tc_fence_after();
+        }
+        const uint32_t row_off = w * (kStepCols * kRowBytes);
 #pragma unroll 1
-  for (int n = 0; n < g.count; ++n) {
-    const uint32_t par = static_cast<uint32_t>(n) & 1u;
-    refresh();
-    const uint32_t s16 = smem16(smem_base + p.off_stage + st.stage * kQStageBytes);
-    const bool has_next = n + 1 < g.count;
-    Ring nx = st;
-    nx.advance();
-    const uint32_t n16 = smem16(smem_base + p.off_stage + nx.stage * kQStageBytes);
-    // the accumulators of the previous job have been read out
-    if (n > 0) {
-      if (!qwait(bar(qbAccFree), par ^ 1u, ctx, 62)) return;
+        for (uint32_t k = 0; k < 2u; ++k) {
+          mma_ss(tw + kQTmS, desc16_at(dk64, n16, kK + 32u * k), desc16_at(dk64, n16, kQ + row_off + 32u * k), idesc_s, k);
+          mma_ss(tw + kQTmDP, desc16_at(dk64, n16, kV + 32u * k), desc16_at(dk64, n16, kDO + row_off + 32u * k), idesc_s,
+                 k);
+        }
+        mma_commit(bar(qbSFull + static_cast<int>(w)));
+      }
     }
-    if (!qwait(bar(qbPReady + 0), par, ctx, 64)) return;
-    tc_fence_after();
-    issue_acc(W0{}, s16);
-    // the next job's scores of step 0 go over this job's P^T / dS^T of the step (the tensor core
-    // works in issue order), so that warpgroup 0 can go on while the rest is issued
-    if (has_next) {
-      if (!qwait(bar(qbReady + nx.stage), nx.phase, ctx, 66)) return;
-      tc_fence_after();
-      issue_sdp(W0{}, n16);
+    if (n >= 0) {
+      // dQ^ = dS K^ over the 128 keys of the block (the previous job's dQ has been read out)
+      if (n > 0) {
+        if (!qwait(bar(qbAccFreeQ), par ^ 1u, ctx, 63)) return;
+      }
+#pragma unroll 1
+      for (uint32_t k = 0; k < 8u; ++k)
+        mma_ss(tmem + kQTmDQ, desc16_at(dds, ds16_c, k * 2048u), desc16_at(dm64, s16, kK + k * 1024u), idesc_dq, k);
+      mma_commit(bar(qbAccFull));
+      mma_commit(bar(qbDsFree));
+      // the stage of job n: the one before `st`
+      mma_commit(bar(qbFree + static_cast<int>(st.stage == 0u ? p.n_stages - 1 : st.stage - 1u)));
     }
-    if (!qwait(bar(qbPReady + 1), par, ctx, 65)) return;
-    tc_fence_after();
-    issue_acc(W1{}, s16);
-    if (has_next) issue_sdp(W1{}, n16);
-    // dQ^ = dS K^ over the 128 keys of the block (the previous job's dQ has been read out)
-    if (n > 0) {
-      if (!qwait(bar(qbAccFreeQ), par ^ 1u, ctx, 63)) return;
-    }
-#pragma unroll
-    for (uint32_t k = 0; k < 8u; ++k)
-      mma_ss(tm + kQTmDQ, desc16_at(dds, ds16, k * 2048u), desc16_at(dm64, s16, kK + k * 1024u), idesc_dq, k);
-    mma_commit(bar(qbAccFull));
-    mma_commit(bar(qbDsFree));
-    mma_commit(bar(qbFree + st.stage));
-    st = nx;
+    s16 = n16;
+    if (has_next) st.advance();
   }
 }
 
