@@ -818,7 +818,7 @@ __global__ void __launch_bounds__(kQuadThreads, 1) bwd_quad_kernel(const __grid_
   // 640 threads start with 96 registers each.  setmaxnreg only moves registers inside what the
   // CTA was given at launch (an increase beyond it would wait for ever), so the four budgets
   // below must not add up to more than 640 x 96.
-  constexpr uint32_t kRegCompute = 112, kRegEpilogue = 112, kRegPrepare = 104, kRegIssue = 40;
+  constexpr uint32_t kRegCompute = 96, kRegEpilogue = 128, kRegPrepare = 112, kRegIssue = 40;
   static_assert(2 * 128 * kRegCompute + 128 * (kRegEpilogue + kRegPrepare + kRegIssue) <= kQuadThreads * 96,
                 "register budgets exceed the launch allocation");
   // (setmaxnreg.inc below what a thread already has, or .dec above it, is an illegal instruction)
