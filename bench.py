@@ -250,7 +250,7 @@ def run_reference(args, w, rank):
               f"({'the installed reference' if kind == 'reference' else 'port of the reference'}) on host cores")
     line = dict(impl="reference", metric=METRIC, value=val, unit=UNIT, n_gpus=args.gpus, steps=args.steps,
                 warmup=warm, ms_per_step=el / args.steps * 1e3, higher_is_better=True,
-                scaling="strong" if args.gpus > 1 else "weak", vs_baseline=None, dtype="f32", data="synthetic",
+                scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
                 config=dict(workload=w.name, images_per_step=images, images=w.batch, windows_per_image=w.nw,
                             heads=w.heads, n=w.n, head_dim=w.head_dim, full_workload_per_step=images == w.batch),
                 cpu_baseline=dict(value=val, unit=UNIT, cores=torch.get_num_threads(), kind=kind, sample=sample),
@@ -576,7 +576,7 @@ def main():
 
     launches = 4 if world == 1 else 5      # forward; table transpose, backward, partial sums; (+ cross-GPU sum and cast)
     line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=warmup,
-                ms_per_step=ms_step, higher_is_better=True, scaling="weak" if world == 1 else "strong",
+                ms_per_step=ms_step, higher_is_better=True, scaling="strong",
                 vs_baseline=None, dtype=w.dtype, data="synthetic",
                 config=dict(workload=w.name, inputs=args.inputs, images=w.batch, images_on_rank0=n_img,
                             windows_per_image=w.nw, heads=w.heads, n=w.n, head_dim=w.head_dim,
