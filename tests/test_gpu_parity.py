@@ -267,6 +267,30 @@ def test_both_forward_kernels_for_windows_of_129_to_256_tokens(window, dtype, kw
     check(w, got, ref, ins)
 
 
+@pytest.mark.parametrize("kw", [dict(with_mask=False), dict(with_bias=False)], ids=["bias_only", "mask_only"])
+def test_forward_with_one_table_repeats_bitwise(kw, dev):
+    """With a single table the table producer runs far ahead of the softmax warps: the
+    configuration in which a table stage released too early was overwritten under a warp that had
+    not read it yet (wrong rows of one warp, in the second unit of a CTA, one launch in three).
+    More units than CTAs, a dozen launches, every one bitwise equal to the first and lse equal to
+    the general kernel's."""
+    from flash_window_attention_v2_b200 import kernels as K
+    w = Workload("w16", batch=7, nw=16, heads=3, window=16, dtype="bf16")
+    t = make_inputs(w, seed=0, device=dev, **kw)
+
+    def fwd(variant):
+        return K._flash_attn_forward(t["q"], t["k"], t["v"], t["logit_scale"], bias=t["bias"], mask=t["mask"],
+                                     scale_type="tensor", _variant=variant)
+    o_gen, l_gen, _ = fwd(32)
+    o0, l0, _ = fwd(0)
+    for _ in range(12):
+        o, l, _ = fwd(0)
+        assert torch.equal(o, o0) and torch.equal(l, l0)
+    K.check_device_status(dev)
+    assert float((l0 - l_gen).abs().max()) < 1e-3
+    assert float((o0.float() - o_gen.float()).abs().max()) < 0.05
+
+
 def test_forward_rows_without_any_admissible_key(dev):
     """The reference's own benchmark inputs (masks of 0 / -inf drawn at random, N(0, 1) logit scale):
     both forward kernels agree on which rows have lse = -inf and on everything else."""
