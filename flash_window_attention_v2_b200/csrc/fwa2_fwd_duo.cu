@@ -32,7 +32,6 @@ constexpr uint32_t kDuoTmemCols = 256;   // 128 per warpgroup (80 used)
 constexpr uint32_t kDuoTmS = 0;          // 32 columns: scores of one step
 constexpr uint32_t kDuoTmO = 32;         // 32 columns: running output
 constexpr uint32_t kDuoTmP = 64;         // 16 columns: 32 probabilities, 16 bit, two per column
-constexpr uint32_t kDuoMaxTableStages = 4;
 constexpr uint32_t kDuoTableStageBytes = 2u * kTableTileBytes;
 // The reference maximum of a row is raised when the row maximum exceeds it by more than this
 // (natural-log units; e^8 < 2^12, far inside the range of fp16 probabilities and fp32 sums).
