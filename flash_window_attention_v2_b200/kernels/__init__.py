@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import threading
 
 import torch
 
@@ -92,15 +93,64 @@ def check_device_status(device=None) -> None:
         raise DeviceTimeoutError(_describe(st))
 
 
-def _t4(x: torch.Tensor) -> _lib.Tensor4:
-    return _lib.Tensor4(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2))
+def _t4(dst: _lib.Tensor4, x: torch.Tensor) -> None:
+    """Fill a tensor descriptor of an argument block in place."""
+    st = x.stride()
+    dst.ptr, dst.stride_bw, dst.stride_h, dst.stride_n = x.data_ptr(), st[0], st[1], st[2]
+
+
+# One argument block per thread and direction, reused from call to call (the forward runs on the
+# caller's thread, the backward on an autograd engine thread; the library reads the block during
+# the call only).
+_tls = threading.local()
+
+
+def _fwd_block() -> _lib.FwdArgs:
+    a = getattr(_tls, "fwd", None)
+    if a is None:
+        a = _tls.fwd = _lib.FwdArgs()
+        a.struct_size = C.sizeof(_lib.FwdArgs)
+        a.abi_version = _lib.FWA2_ABI_VERSION
+    return a
+
+
+def _bwd_block() -> _lib.BwdArgs:
+    a = getattr(_tls, "bwd", None)
+    if a is None:
+        a = _tls.bwd = _lib.BwdArgs()
+        a.struct_size = C.sizeof(_lib.BwdArgs)
+        a.abi_version = _lib.FWA2_ABI_VERSION
+    return a
 
 
 def _tma_ok(x: torch.Tensor) -> bool:
     """Inner stride 1, every other stride a multiple of 8 elements, 16-byte aligned base."""
-    if x.stride(-1) != 1 or x.data_ptr() % 16 != 0:
+    if x.data_ptr() % 16 != 0:
+        return False
+    if x.is_contiguous():          # the common case, one call: rows of 32 elements, so every
+        return x.shape[-1] % 8 == 0   # outer stride is a multiple of 8 as well
+    if x.stride(-1) != 1:
         return False
     return all(x.shape[i] == 1 or (x.stride(i) > 0 and x.stride(i) % 8 == 0) for i in range(3))
+
+
+class _on_device:
+    """`with torch.cuda.device(dev)` only when `dev` is not already current (the context manager
+    costs several microseconds of a call whose kernels take a few tens)."""
+    __slots__ = ("ctx",)
+
+    def __init__(self, device: torch.device):
+        idx = device.index
+        self.ctx = None if (idx is None or idx == torch.cuda.current_device()) else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+        return False
 
 
 def _rows(x: torch.Tensor) -> torch.Tensor:
@@ -120,7 +170,8 @@ def _table(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 
 def _stream(device) -> C.c_void_p:
-    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return C.c_void_p(torch._C._cuda_getCurrentRawStream(idx))
 
 
 def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="scalar",
@@ -165,13 +216,11 @@ def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="
     bias_t = _table(bias, q.dtype) if bias is not None else None
     mask_t = _table(mask, q.dtype) if mask is not None else None
 
-    a = _lib.FwdArgs()
-    a.struct_size = C.sizeof(_lib.FwdArgs)
-    a.abi_version = _lib.FWA2_ABI_VERSION
+    a = _fwd_block()
     a.dtype = _DTYPES[q.dtype]
     a.bw, a.heads, a.n, a.head_dim = batch_window_size, n_heads, seqlen_q, d
     a.n_windows = n_windows
-    a.q, a.k, a.v, a.o = _t4(qc), _t4(kc), _t4(vc), _t4(o)
+    _t4(a.q, qc), _t4(a.k, kc), _t4(a.v, vc), _t4(a.o, o)
     a.lse = lse.data_ptr()
     a.lse_stride_bw, a.lse_stride_h = lse.stride(0), lse.stride(1)
     a.logit_scale = logit_scale.data_ptr()
@@ -183,10 +232,8 @@ def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="
     a.status = _status(q.device).data_ptr()
     a.variant = _variant
     a.max_ctas = _max_ctas
-    if _trace is not None:      # development builds of the library only
-        a.developer0 = _trace.data_ptr()
-        a.developer1 = _trace.numel() // 4
-    with torch.cuda.device(q.device):
+    a.developer0, a.developer1 = (_trace.data_ptr(), _trace.numel() // 4) if _trace is not None else (None, 0)
+    with _on_device(q.device):
         _lib.check(_lib.lib().fwa2_forward(C.byref(a), _stream(q.device)), "fwa2_forward")
     return o, lse, logit_scale
 
@@ -240,7 +287,7 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
         dscale.shape, device=dscale.device, dtype=dscale.dtype)
 
     L = _lib.lib()
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         ws_bytes = L.fwa2_bwd_workspace_bytes(batch_window_size, n_heads, seqlen_q, n_windows,
                                               1 if has_bias else 0, 1 if mask is not None else 0)
         assert ws_bytes > 0
@@ -250,14 +297,12 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
         else:
             workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
 
-        a = _lib.BwdArgs()
-        a.struct_size = C.sizeof(_lib.BwdArgs)
-        a.abi_version = _lib.FWA2_ABI_VERSION
+        a = _bwd_block()
         a.dtype = _DTYPES[q.dtype]
         a.bw, a.heads, a.n, a.head_dim = batch_window_size, n_heads, seqlen_q, d
         a.n_windows = n_windows
-        a.q, a.k, a.v, a.o, a.dout = _t4(qc), _t4(kc), _t4(vc), _t4(oc), _t4(doc)
-        a.dq, a.dk, a.dv = _t4(outs[0]), _t4(outs[1]), _t4(outs[2])
+        _t4(a.q, qc), _t4(a.k, kc), _t4(a.v, vc), _t4(a.o, oc), _t4(a.dout, doc)
+        _t4(a.dq, outs[0]), _t4(a.dk, outs[1]), _t4(a.dv, outs[2])
         a.lse = lse.data_ptr()
         a.lse_stride_bw, a.lse_stride_h = lse.stride(0), lse.stride(1)
         a.logit_scale = logit_scale.data_ptr()
@@ -274,9 +319,7 @@ def _flash_attn_backward(do, q, k, v, logit_scale, o, lse, dq, dk, dv, dscale, d
         a.status = _status(q.device).data_ptr()
         a.variant = _variant
         a.max_ctas = _max_ctas
-        if _trace is not None:      # development builds of the library only
-            a.developer0 = _trace.data_ptr()
-            a.developer1 = _trace.numel() // 4
+        a.developer0, a.developer1 = (_trace.data_ptr(), _trace.numel() // 4) if _trace is not None else (None, 0)
         _lib.check(L.fwa2_backward(C.byref(a), _stream(q.device)), "fwa2_backward")
         _mirror_status(q.device)
 
