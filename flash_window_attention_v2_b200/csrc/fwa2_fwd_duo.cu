@@ -20,7 +20,7 @@
 // appear once), compact waits, and kernel instantiations per table combination instead of
 // run-time branches in the step.
 // Replaces flash_win_attn_v2/kernels/attn_kernel_forward.py:21-258 (`_fwd_kernel`) for these sizes.
-#define FWA2_NORMALISE_ROLLED 1
+#define FWA2_NORMALISE_ROLLED 0
 #define FWA2_WAIT_INLINE 1
 #include "fwa2_common.cuh"
 
