@@ -18,6 +18,12 @@ SOURCES = ["fwa2_api.cu", "fwa2_fwd.cu", "fwa2_fwd_duo.cu", "fwa2_bwd.cu", "fwa2
 
 FWA2_ABI_VERSION = 1
 FWA2_F16, FWA2_BF16 = 0, 1
+# bits of fwd / bwd args.variant (include/fwa2.h)
+FWA2_FWD_P_IN_SMEM = 1
+FWA2_BWD_SKIP_TABLES = 2
+FWA2_BWD_SKIP_REDUCE = 4
+FWA2_BWD_GENERAL_KERNEL = 16
+FWA2_FWD_GENERAL_KERNEL = 32
 
 
 class Tensor4(C.Structure):

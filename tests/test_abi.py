@@ -25,6 +25,18 @@ def test_every_declared_symbol_is_exported(lib):
         assert hasattr(lib, name), name
 
 
+def test_variant_bits_match_the_header():
+    """The variant bits the Python binding names are the ones include/fwa2.h defines, and no two
+    of them share a bit."""
+    header = open(os.path.join(ROOT, "include", "fwa2.h")).read()
+    defined = {name: int(value) for name, value in re.findall(r"#define\s+(FWA2_(?:FWD|BWD)_[A-Z_]+)\s+(\d+)", header)}
+    assert defined, "no variant bits found in the header"
+    for name, value in defined.items():
+        assert getattr(_lib, name) == value, name
+        assert value & (value - 1) == 0, name          # a single bit
+    assert len(set(defined.values())) == len(defined)
+
+
 def test_struct_sizes_match_header_layout():
     # plain-C layout: 4 + 4 + 4 + 4*4 + 4 = 32 bytes of scalars, then 8-byte aligned members
     assert C.sizeof(_lib.Tensor4) == 32

@@ -251,7 +251,7 @@ def test_both_backward_kernels_for_mid_size_windows(variant, dev):
                             mask=t["mask"]))
 
 
-@pytest.mark.parametrize("variant", [0, 32], ids=["two_warpgroup_kernel", "general_kernel"])
+@pytest.mark.parametrize("variant", [0, 32], ids=["two_warpgroup_kernel", "general_kernel"])   # 32 = FWA2_FWD_GENERAL_KERNEL
 @pytest.mark.parametrize("window,dtype,kw", [
     (16, "bf16", {}), (16, "fp16", {}), (12, "bf16", {}), (14, "fp16", {}), (13, "bf16", {}),
     (16, "bf16", dict(with_mask=False)), (16, "fp16", dict(with_bias=False)),
