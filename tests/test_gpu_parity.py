@@ -291,6 +291,34 @@ def test_forward_with_one_table_repeats_bitwise(kw, dev):
     assert float((o0.float() - o_gen.float()).abs().max()) < 0.05
 
 
+@pytest.mark.parametrize("n,dtype", [(129, torch.bfloat16), (161, torch.float16), (200, torch.bfloat16),
+                                     (255, torch.float16), (127, torch.bfloat16), (257, torch.float16)])
+def test_token_counts_that_are_no_squares(n, dtype, dev):
+    """The boundary takes any N, not only w * w: ragged last steps, last tiles and table pitches
+    that have to be padded, on both sides of the sizes at which the kernels change (128 / 129,
+    256 / 257).  Forward and backward through the boundary functions against the oracle."""
+    from flash_window_attention_v2_b200 import kernels as K
+    g = torch.Generator(device="cpu").manual_seed(n)
+    bw, h, nw = 6, 2, 3
+    q, k, v, do = (torch.randn(bw, h, n, 32, generator=g).to(dtype).to(dev) for _ in range(4))
+    bias = (16 * torch.sigmoid(torch.randn(h, n, n, generator=g))).to(dtype).to(dev)
+    mask = torch.where(torch.rand(nw, n, n, generator=g) < 0.3, torch.tensor(-100.0), torch.tensor(0.0))
+    mask[:, torch.arange(n), torch.arange(n)] = 0
+    mask = mask.to(dtype).to(dev)
+    ls = torch.full((h, 1, 1), math.log(10.0)).to(dtype).to(dev)
+    o, lse, _ = K._flash_attn_forward(q, k, v, ls, bias=bias, mask=mask, scale_type="tensor")
+    dq, dk, dv = (torch.empty_like(x) for x in (q, k, v))
+    ds, db = torch.empty_like(ls), torch.empty_like(bias)
+    K._flash_attn_backward(do, q, k, v, ls, o, lse, dq, dk, dv, ds, db, bias=bias, mask=mask, scale_type="tensor")
+    K.check_device_status(dev)
+    ref = orc.forward_backward(_f(q), _f(k), _f(v), _f(do), _f(ls), _f(bias), _f(mask), dtype=np.float32)
+    tol = TOL["bf16" if dtype == torch.bfloat16 else "fp16"]
+    for key, got in dict(o=o, dq=dq, dk=dk, dv=dv, dbias=db).items():
+        assert np.isfinite(_f(got)).all(), key
+        assert orc.rel_err(_f(got), ref[key]) < tol[key], (key, orc.rel_err(_f(got), ref[key]))
+    assert np.abs(_f(lse)[..., :n] - ref["lse"]).max() < (4e-2 if dtype == torch.bfloat16 else 5e-3)
+
+
 def test_forward_rows_without_any_admissible_key(dev):
     """The reference's own benchmark inputs (masks of 0 / -inf drawn at random, N(0, 1) logit scale):
     both forward kernels agree on which rows have lse = -inf and on everything else."""
