@@ -574,7 +574,11 @@ def main():
     if world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(w)
 
-    launches = 4 if world == 1 else 5      # forward; table transpose, backward, partial sums; (+ cross-GPU sum and cast)
+    # forward (+ the pass that adds bias and mask into one fp32 table where the library uses one);
+    # table transpose, backward, partial sums; (+ cross-GPU sum and cast)
+    from flash_window_attention_v2_b200 import _lib
+    combined = _lib.lib().fwa2_fwd_workspace_bytes(n_img * w.nw, w.heads, w.n, w.nw, 1, 1, 0) != 0
+    launches = (4 if world == 1 else 5) + (1 if combined else 0)
     line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=warmup,
                 ms_per_step=ms_step, higher_is_better=True, scaling="strong",
                 vs_baseline=None, dtype=w.dtype, data="synthetic",

@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 SOURCES = ["fwa2_api.cu", "fwa2_fwd.cu", "fwa2_fwd_duo.cu", "fwa2_bwd.cu", "fwa2_bwd_quad.cu", "fwa2_reduce.cu", "fwa2_selftest.cu",
            "fwa2_static_scratch.cu", "fwa2_cpb_bias.cu", "fwa2_peer_reduce.cu"]
 
-FWA2_ABI_VERSION = 1
+FWA2_ABI_VERSION = 2
 FWA2_F16, FWA2_BF16 = 0, 1
 # bits of fwd / bwd args.variant (include/fwa2.h)
 FWA2_FWD_P_IN_SMEM = 1
@@ -24,6 +24,8 @@ FWA2_BWD_SKIP_TABLES = 2
 FWA2_BWD_SKIP_REDUCE = 4
 FWA2_BWD_GENERAL_KERNEL = 16
 FWA2_FWD_GENERAL_KERNEL = 32
+FWA2_FWD_COMBINE_TABLES = 64
+FWA2_FWD_SEPARATE_TABLES = 128
 
 
 class Tensor4(C.Structure):
@@ -41,6 +43,7 @@ class FwdArgs(C.Structure):
         ("logit_scale", C.c_void_p), ("scale_is_tensor", C.c_int32),
         ("bias", C.c_void_p), ("mask", C.c_void_p),
         ("bias_row_stride", C.c_int64), ("mask_row_stride", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p), ("variant", C.c_int32), ("max_ctas", C.c_int32),
         ("developer0", C.c_void_p), ("developer1", C.c_int32), ("reserved0", C.c_int32),
     ]
@@ -65,7 +68,7 @@ class BwdArgs(C.Structure):
 
 
 EXPORTS = ("fwa2_abi_version", "fwa2_strerror", "fwa2_last_cuda_error", "fwa2_forward",
-           "fwa2_bwd_workspace_bytes", "fwa2_backward", "fwa2_finalize_grads",
+           "fwa2_fwd_workspace_bytes", "fwa2_bwd_workspace_bytes", "fwa2_backward", "fwa2_finalize_grads",
            "fwa2_selftest_mma", "fwa2_backward_static_scratch",
            "fwa2_cpb_bias_forward", "fwa2_cpb_bias_backward", "fwa2_peer_reduce_finalize")
 
@@ -113,6 +116,8 @@ def lib() -> C.CDLL:
         L.fwa2_last_cuda_error.restype = C.c_int
         L.fwa2_forward.restype = C.c_int
         L.fwa2_forward.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
+        L.fwa2_fwd_workspace_bytes.restype = C.c_size_t
+        L.fwa2_fwd_workspace_bytes.argtypes = [C.c_int32] * 7
         L.fwa2_bwd_workspace_bytes.restype = C.c_size_t
         L.fwa2_bwd_workspace_bytes.argtypes = [C.c_int32] * 6
         L.fwa2_backward.restype = C.c_int

@@ -14,6 +14,9 @@ namespace fwa2 {
 cudaError_t launch_fwd(const FwdParams& p, int dtype_is_bf16, int p_in_tmem, int grid,
                        cudaStream_t stream);
 cudaError_t launch_fwd_duo(const FwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
+cudaError_t launch_combine_tables(const void* bias, long long bias_pitch, const void* mask, long long mask_pitch,
+                                  float* out, int n, int heads, int n_windows, int pitch, int dtype_is_bf16,
+                                  cudaStream_t stream);
 cudaError_t launch_bwd(const BwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
 cudaError_t launch_bwd_quad(const QuadParams& p, int dtype_is_bf16, int grid, cudaStream_t stream);
 int quad_max_active_clusters(int dtype_is_bf16, int cluster, uint32_t smem_bytes);
@@ -132,6 +135,39 @@ int encode_table3(CUtensorMap* m, const void* ptr, int dtype, int planes, int ro
     return FWA2_ERR_TENSOR_MAP;
   }
   return FWA2_OK;
+}
+
+// (planes, rows, pitch) fp32 table -> 3-D map (cols, rows, planes), box (32, 128, 1): rows of 128
+// bytes, 128-byte swizzle.
+int encode_comb3(CUtensorMap* m, const void* ptr, int planes, int rows, int cols, int pitch) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return FWA2_ERR_DRIVER;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(planes)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(pitch) * 4u,
+                           static_cast<cuuint64_t>(pitch) * 4u * static_cast<cuuint64_t>(rows)};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kChunkCols), static_cast<cuuint32_t>(kTileRows), 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return FWA2_ERR_TENSOR_MAP;
+  }
+  return FWA2_OK;
+}
+
+// The forward kernel for windows of 129 to 256 tokens can read ONE fp32 table, bias + mask, per
+// (window type, head) instead of the two 16-bit tables: two conversions and an addition less per
+// score.  Building that table costs a pass of its own (4 * nW * H * N * pitch bytes written), which
+// pays once every table is used by enough units, i.e. images.
+constexpr int kCombMinImages = 24;
+int comb_pitch(int n) { return ((n + 31) / 32) * 32; }
+bool comb_applies(int bw, int n, int n_windows, bool has_bias, bool has_mask, int variant) {
+  if (!has_bias || !has_mask || n <= 128 || n > 256 || n_windows <= 0 || (bw % n_windows) != 0) return false;
+  if (variant & (FWA2_FWD_SEPARATE_TABLES | FWA2_FWD_GENERAL_KERNEL | FWA2_FWD_P_IN_SMEM)) return false;
+  return (variant & FWA2_FWD_COMBINE_TABLES) != 0 || bw / n_windows >= kCombMinImages;
 }
 
 int check_common(int dtype, int bw, int heads, int n, int head_dim, int n_windows, bool has_mask) {
@@ -257,6 +293,13 @@ extern "C" const char* fwa2_strerror(int code) {
   }
 }
 
+extern "C" size_t fwa2_fwd_workspace_bytes(int32_t bw, int32_t heads, int32_t n, int32_t n_windows,
+                                           int32_t has_bias, int32_t has_mask, int32_t variant) {
+  if (bw <= 0 || heads <= 0 || heads > 192 || n <= 0) return 0;
+  if (!comb_applies(bw, n, n_windows, has_bias != 0, has_mask != 0, variant)) return 0;
+  return align256(static_cast<size_t>(n_windows) * heads * n * comb_pitch(n) * 4u);
+}
+
 extern "C" int fwa2_forward(const fwa2_fwd_args* a, void* stream) {
   if (a == nullptr) return FWA2_ERR_NULL;
   if (a->struct_size != sizeof(fwa2_fwd_args) || a->abi_version != FWA2_ABI_VERSION) return FWA2_ERR_ABI;
@@ -326,6 +369,29 @@ extern "C" int fwa2_forward(const fwa2_fwd_args* a, void* stream) {
       int grid = dev.sm_count * 2;
       if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
       if (grid > p.n_jobs) grid = p.n_jobs;
+      // ---- one fp32 table (bias + mask) per (window type, head), when it pays ----
+      const size_t comb_bytes = fwa2_fwd_workspace_bytes(a->bw, a->heads, a->n, a->n_windows, has_bias, has_mask,
+                                                         a->variant);
+      if (comb_bytes != 0) {
+        const bool usable = a->workspace != nullptr && a->workspace_bytes >= comb_bytes &&
+                            (reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0;
+        if (!usable && (a->variant & FWA2_FWD_COMBINE_TABLES)) return FWA2_ERR_WORKSPACE;
+        if (usable) {
+          const int pitch = comb_pitch(a->n);
+          if ((rc = encode_comb3(&p.tm_bias, a->workspace, a->n_windows * a->heads, a->n, a->n, pitch)) != FWA2_OK)
+            return rc;
+          const cudaError_t ce = launch_combine_tables(a->bias, a->bias_row_stride, a->mask, a->mask_row_stride,
+                                                       static_cast<float*>(a->workspace), a->n, a->heads,
+                                                       a->n_windows, pitch, a->dtype == FWA2_BF16,
+                                                       static_cast<cudaStream_t>(stream));
+          if (ce != cudaSuccess) {
+            g_last_cuda_error = static_cast<int>(ce);
+            return FWA2_ERR_LAUNCH;
+          }
+          p.comb = 1;
+          p.n_img = a->bw / a->n_windows;
+        }
+      }
       const cudaError_t e = launch_fwd_duo(p, a->dtype == FWA2_BF16, grid, static_cast<cudaStream_t>(stream));
       if (e != cudaSuccess) {
         g_last_cuda_error = static_cast<int>(e);

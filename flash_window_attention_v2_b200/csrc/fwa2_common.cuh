@@ -71,6 +71,10 @@ struct FwdParams {
   int BW, H, N, nW;
   int has_bias, has_mask;
   int pair_mode;
+  int comb;                       // tm_bias describes the fp32 table bias + mask, (N, N, nW * H), box
+                                  // (32, 128, 1), 128-byte swizzle, and the units are walked table by
+                                  // table: job = (window type * H + head) * n_img + image
+  int n_img;                      // BW / nW
   int n_jobs;                     // units, or pairs of units in pair mode
   int n_kv_stages;                // 1 or 2
   int n_bm_stages;

@@ -127,7 +127,7 @@ __device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* m, int c0, in
 // ------------------------------------------------------------------------------------------------
 // Softmax warpgroups
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool kBias, bool kMask>
+template <typename T, bool kBias, bool kMask, bool kComb>
 __device__ __forceinline__ void duo_softmax_role(const FwdParams& p, uint32_t smem_base, uint32_t bars,
                                                  uint32_t tmem, const WaitCtx& ctx, const float* scale_tab) {
   constexpr bool kTable = kBias || kMask;
@@ -139,7 +139,9 @@ __device__ __forceinline__ void duo_softmax_role(const FwdParams& p, uint32_t sm
   const uint32_t rows_kv = static_cast<uint32_t>((N + 63) / 64) * 64u;
   const uint32_t bar_s_full = bars + 8u * (dbSFull + wg), bar_s_free = bars + 8u * (dbSFree + wg);
   const uint32_t bar_p_full = bars + 8u * (dbPFull + wg), bar_pv = bars + 8u * (dbPvDone + wg);
-  const uint32_t row_off = t * 64u, row_sw = (t >> 1) & 3u;
+  // where thread t finds its row of a table chunk: rows of 64 bytes (64-byte swizzle) per 16-bit
+  // table, rows of 128 bytes (128-byte swizzle) in the combined fp32 table
+  const uint32_t row_off = kComb ? t * 128u : t * 64u, row_sw = kComb ? (t & 7u) : ((t >> 1) & 3u);
   const float2 log2e2 = make_float2(kLog2e, kLog2e);
 
   TableRing ring{wg, 0u, static_cast<uint32_t>(p.n_bm_stages)};
@@ -192,7 +194,15 @@ __device__ __forceinline__ void duo_softmax_role(const FwdParams& p, uint32_t sm
     }
     DPROF_SEG(7);
     if (!have_job) break;
-    const int bw = job / H, h = job - bw * H;
+    int bw, h;
+    if constexpr (kComb) {
+      const int plane = job / p.n_img, wt = plane / H;
+      h = plane - wt * H;
+      bw = (job - plane * p.n_img) * p.nW + wt;
+    } else {
+      bw = job / H;
+      h = job - bw * H;
+    }
     const float scale = scale_tab[h];
     const float2 scale2 = make_float2(scale, scale);
     m_ref = 0.f;
@@ -207,15 +217,21 @@ __device__ __forceinline__ void duo_softmax_role(const FwdParams& p, uint32_t sm
       uint32_t r[32];
       tmem_ld32(tm + kDuoTmS, r);
       // (the table words are fetched while the tensor-memory load is in flight)
-      uint32_t wb[4][4], wm[4][4];
+      uint32_t wb[4][4], wm[4][4];   // 16-bit tables: 8 columns per 16 bytes
+      uint32_t wc[8][4];             // combined fp32 table: 4 columns per 16 bytes
       if constexpr (kTable) {
         const uint32_t base = smem_base + p.off_bm + ring.stage * kDuoTableStageBytes + row_off;
         if (!dwait_warp(bars + 8u * (dbTFull + ring.stage), ring.phase, ctx, 13)) return;
+        if constexpr (kComb) {
 #pragma unroll
-        for (uint32_t ch = 0; ch < 4u; ++ch) {
-          const uint32_t off = base + ((ch ^ row_sw) << 4);
-          if constexpr (kBias) lds128(off, wb[ch]);
-          if constexpr (kMask) lds128(off + kTableTileBytes, wm[ch]);
+          for (uint32_t ch = 0; ch < 8u; ++ch) lds128(base + ((ch ^ row_sw) << 4), wc[ch]);
+        } else {
+#pragma unroll
+          for (uint32_t ch = 0; ch < 4u; ++ch) {
+            const uint32_t off = base + ((ch ^ row_sw) << 4);
+            if constexpr (kBias) lds128(off, wb[ch]);
+            if constexpr (kMask) lds128(off + kTableTileBytes, wm[ch]);
+          }
         }
       }
       tmem_wait_ld();
@@ -227,13 +243,16 @@ __device__ __forceinline__ void duo_softmax_role(const FwdParams& p, uint32_t sm
 #pragma unroll
       for (int e = 0; e < 32; e += 2) {
         float2 x2 = make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1]));
-        if constexpr (kBias) {
+        if constexpr (kComb) {
+          x2 = __ffma2_rn(x2, scale2, make_float2(__uint_as_float(wc[e >> 2][e & 3]),
+                                                  __uint_as_float(wc[e >> 2][(e & 3) + 1])));
+        } else if constexpr (kBias) {
           const uint32_t wv = wb[e >> 3][(e >> 1) & 3];
           x2 = __ffma2_rn(x2, scale2, make_float2(Elem<T>::lo(wv), Elem<T>::hi(wv)));
         } else {
           x2 = __fmul2_rn(x2, scale2);
         }
-        if constexpr (kMask) {
+        if constexpr (kMask && !kComb) {
           const uint32_t wv = wm[e >> 3][(e >> 1) & 3];
           x2 = __fadd2_rn(x2, make_float2(Elem<T>::lo(wv), Elem<T>::hi(wv)));
         }
@@ -405,9 +424,22 @@ __device__ __forceinline__ void duo_load_role(const FwdParams& p, uint32_t smem_
   int b_job = blockIdx.x, b_e = 0;
   TableRing b_ring{0u, 0u, static_cast<uint32_t>(p.n_bm_stages)};
   bool a_done = a_job >= p.n_jobs, b_done = !any_table || b_job >= p.n_jobs;
-  int a_bw = a_job / H, a_h = a_job - a_bw * H;
-  int b_bw = b_job / H, b_h = b_job - b_bw * H;
-  int b_mw = p.has_mask ? b_bw % p.nW : 0;
+  // unit of a job: (window, head); in combined-table order also the table plane
+  auto unit_of = [&](int job, int& bw, int& h, int& plane) {
+    if (p.comb) {
+      plane = job / p.n_img;
+      const int wt = plane / H;
+      h = plane - wt * H;
+      bw = (job - plane * p.n_img) * p.nW + wt;
+    } else {
+      bw = job / H;
+      h = job - bw * H;
+      plane = p.has_mask ? bw % p.nW : 0;   // the mask's window type
+    }
+  };
+  int a_bw = 0, a_h = 0, a_plane = 0, b_bw = 0, b_h = 0, b_mw = 0;
+  if (!a_done) unit_of(a_job, a_bw, a_h, a_plane);
+  if (!b_done) unit_of(b_job, b_bw, b_h, b_mw);
 
   uint32_t idle = 0, t0 = 0;
 #pragma unroll 1
@@ -432,8 +464,7 @@ __device__ __forceinline__ void duo_load_role(const FwdParams& p, uint32_t smem_
           a_job += gridDim.x;
           a_done = a_job >= p.n_jobs;
           if (!a_done) {
-            a_bw = a_job / H;
-            a_h = a_job - a_bw * H;
+            unit_of(a_job, a_bw, a_h, a_plane);
             // K, Q and V of the unit after this one: into L2 now, so that the loads that have to
             // wait for this unit's last products find them there
 #pragma unroll 1
@@ -455,22 +486,22 @@ __device__ __forceinline__ void duo_load_role(const FwdParams& p, uint32_t smem_
         const int c0 = (b_e >> 1) * kDuoStep;
         const int r0 = (b_e & 1) * kTileRows;
         mbar_arrive_expect_tx(full, table_bytes);
+        if (p.comb) {
+          tma_load_3d(base, &p.tm_bias, full, c0, r0, b_mw);   // one box of 128 rows x 32 fp32
+        } else {
 #pragma unroll 1
-        for (int b = 0; b < 2; ++b) {
-          if (p.has_bias) tma_load_3d(base + b * kBoxBytes, &p.tm_bias, full, c0, r0 + b * kBoxRows, b_h);
-          if (p.has_mask)
-            tma_load_3d(base + kTableTileBytes + b * kBoxBytes, &p.tm_mask, full, c0, r0 + b * kBoxRows, b_mw);
+          for (int b = 0; b < 2; ++b) {
+            if (p.has_bias) tma_load_3d(base + b * kBoxBytes, &p.tm_bias, full, c0, r0 + b * kBoxRows, b_h);
+            if (p.has_mask)
+              tma_load_3d(base + kTableTileBytes + b * kBoxBytes, &p.tm_mask, full, c0, r0 + b * kBoxRows, b_mw);
+          }
         }
         b_ring.advance(1u);
         if (++b_e >= 2 * KS) {
           b_e = 0;
           b_job += gridDim.x;
           b_done = b_job >= p.n_jobs;
-          if (!b_done) {
-            b_bw = b_job / H;
-            b_h = b_job - b_bw * H;
-            b_mw = p.has_mask ? b_bw % p.nW : 0;
-          }
+          if (!b_done) unit_of(b_job, b_bw, b_h, b_mw);
         }
         progress = true;
       }
@@ -492,7 +523,7 @@ __device__ __forceinline__ void duo_load_role(const FwdParams& p, uint32_t smem_
 }
 
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool kBias, bool kMask>
+template <typename T, bool kBias, bool kMask, bool kComb>
 __global__ void __launch_bounds__(kDuoThreads, 2) fwd_duo_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t tid = threadIdx.x;
@@ -522,7 +553,7 @@ __global__ void __launch_bounds__(kDuoThreads, 2) fwd_duo_kernel(const __grid_co
     tma_prefetch_desc(&p.tm_k);
     tma_prefetch_desc(&p.tm_v);
     if (kBias) tma_prefetch_desc(&p.tm_bias);
-    if (kMask) tma_prefetch_desc(&p.tm_mask);
+    if (kMask && !kComb) tma_prefetch_desc(&p.tm_mask);
   }
   if (warp == 8) {
     tmem_alloc(smem_u32(&tmem_slot), kDuoTmemCols);
@@ -540,7 +571,7 @@ __global__ void __launch_bounds__(kDuoThreads, 2) fwd_duo_kernel(const __grid_co
 
   if (warp < 8) {
     reg_alloc<kDuoRegSoftmax>();
-    duo_softmax_role<T, kBias, kMask>(p, smem_base, bars, tmem, ctx, scale_tab);
+    duo_softmax_role<T, kBias, kMask, kComb>(p, smem_base, bars, tmem, ctx, scale_tab);
   } else {
     reg_dealloc<kDuoRegOther>();
     if (lane == 0) {
@@ -561,6 +592,54 @@ __global__ void __launch_bounds__(kDuoThreads, 2) fwd_duo_kernel(const __grid_co
   if (warp == 8) tmem_dealloc(tmem, kDuoTmemCols);
 }
 
+// ------------------------------------------------------------------------------------------------
+// out[(wt * H + h)][i][j] = float(bias[h][i][j]) + float(mask[wt][i][j]), fp32, rows of `pitch`
+// floats (columns from N on are written as zero).  One thread per 8 columns, 32 threads per row,
+// 8 rows per CTA.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) combine_tables_kernel(const uint16_t* __restrict__ bias, long long bias_pitch,
+                                                             const uint16_t* __restrict__ mask, long long mask_pitch,
+                                                             float* __restrict__ out, int N, int H, int pitch) {
+  const int plane = blockIdx.y, wt = plane / H, h = plane - wt * H;
+  const int row = blockIdx.x * 8 + static_cast<int>(threadIdx.x >> 5);
+  const int col = static_cast<int>(threadIdx.x & 31u) * 8;
+  if (row >= N || col >= pitch) return;
+  float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+  if (col < N) {   // the tables' rows are padded to multiples of 8 elements: the 16 bytes exist
+    const uint4 b = *reinterpret_cast<const uint4*>(bias + (static_cast<long long>(h) * N + row) * bias_pitch + col);
+    const uint4 m = *reinterpret_cast<const uint4*>(mask + (static_cast<long long>(wt) * N + row) * mask_pitch + col);
+    lo = make_float4(Elem<T>::lo(b.x) + Elem<T>::lo(m.x), Elem<T>::hi(b.x) + Elem<T>::hi(m.x),
+                     Elem<T>::lo(b.y) + Elem<T>::lo(m.y), Elem<T>::hi(b.y) + Elem<T>::hi(m.y));
+    hi = make_float4(Elem<T>::lo(b.z) + Elem<T>::lo(m.z), Elem<T>::hi(b.z) + Elem<T>::hi(m.z),
+                     Elem<T>::lo(b.w) + Elem<T>::lo(m.w), Elem<T>::hi(b.w) + Elem<T>::hi(m.w));
+    if (col + 8 > N) {   // the tail of the last group of a row
+      float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (col + i >= N) v[i] = 0.f;
+      lo = make_float4(v[0], v[1], v[2], v[3]);
+      hi = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  }
+  float* dst = out + (static_cast<long long>(plane) * N + row) * pitch + col;
+  *reinterpret_cast<float4*>(dst) = lo;
+  *reinterpret_cast<float4*>(dst + 4) = hi;
+}
+
+cudaError_t launch_combine_tables(const void* bias, long long bias_pitch, const void* mask, long long mask_pitch,
+                                  float* out, int n, int heads, int n_windows, int pitch, int dtype_is_bf16,
+                                  cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>((n + 7) / 8), static_cast<unsigned>(n_windows * heads));
+  const uint16_t* b = static_cast<const uint16_t*>(bias);
+  const uint16_t* m = static_cast<const uint16_t*>(mask);
+  if (dtype_is_bf16)
+    combine_tables_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(b, bias_pitch, m, mask_pitch, out, n, heads, pitch);
+  else
+    combine_tables_kernel<__half><<<grid, 256, 0, stream>>>(b, bias_pitch, m, mask_pitch, out, n, heads, pitch);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_fwd_duo(const FwdParams& p, int dtype_is_bf16, int grid, cudaStream_t stream) {
   auto go = [&](auto kern) -> cudaError_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -571,8 +650,10 @@ cudaError_t launch_fwd_duo(const FwdParams& p, int dtype_is_bf16, int grid, cuda
   };
   auto by_tables = [&](auto type_tag) -> cudaError_t {
     using T = decltype(type_tag);
-    if (p.has_bias) return p.has_mask ? go(fwd_duo_kernel<T, true, true>) : go(fwd_duo_kernel<T, true, false>);
-    return p.has_mask ? go(fwd_duo_kernel<T, false, true>) : go(fwd_duo_kernel<T, false, false>);
+    if (p.comb) return go(fwd_duo_kernel<T, true, true, true>);
+    if (p.has_bias)
+      return p.has_mask ? go(fwd_duo_kernel<T, true, true, false>) : go(fwd_duo_kernel<T, true, false, false>);
+    return p.has_mask ? go(fwd_duo_kernel<T, false, true, false>) : go(fwd_duo_kernel<T, false, false, false>);
   };
   return dtype_is_bf16 ? by_tables(__nv_bfloat16{}) : by_tables(__half{});
 }

@@ -229,6 +229,15 @@ def _flash_attn_forward(q, k, v, logit_scale, bias=None, mask=None, scale_type="
     a.mask = mask_t.data_ptr() if mask_t is not None else None
     a.bias_row_stride = bias_t.stride(1) if bias_t is not None else 0
     a.mask_row_stride = mask_t.stride(1) if mask_t is not None else 0
+    # Scratch for the combined fp32 table (bias + mask); the library asks for it only where it pays:
+    # windows of 129 to 256 tokens with both tables and enough images per window type.
+    workspace, ws_bytes = None, 0
+    if bias_t is not None and mask_t is not None and 128 < seqlen_q <= 256:
+        ws_bytes = _lib.lib().fwa2_fwd_workspace_bytes(batch_window_size, n_heads, seqlen_q, n_windows, 1, 1, _variant)
+        if ws_bytes:
+            workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    a.workspace = workspace.data_ptr() if workspace is not None else None
+    a.workspace_bytes = ws_bytes
     a.status = _status(q.device).data_ptr()
     a.variant = _variant
     a.max_ctas = _max_ctas

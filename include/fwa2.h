@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define FWA2_ABI_VERSION 1
+#define FWA2_ABI_VERSION 2
 
 enum fwa2_dtype { FWA2_F16 = 0, FWA2_BF16 = 1 };
 
@@ -58,6 +58,15 @@ enum fwa2_error {
 #define FWA2_FWD_GENERAL_KERNEL 32 /* forward: windows of 129 to 256 tokens normally run on the
                                     kernel with two softmax warpgroups per CTA (one per 128-row
                                     tile of the unit); this bit selects the general kernel */
+#define FWA2_FWD_COMBINE_TABLES 64 /* forward, bias AND mask, windows of 129 to 256 tokens: add the
+                                    two tables once per call into one fp32 table per (window type,
+                                    head) in the workspace and let the kernel read that (it then
+                                    walks the units table by table).  Without this bit the library
+                                    does so only when the batch holds enough images per window type
+                                    to pay for the extra pass (fwa2_fwd_workspace_bytes tells), and
+                                    falls back to separate tables if the workspace is missing;
+                                    with this bit a missing workspace is FWA2_ERR_WORKSPACE */
+#define FWA2_FWD_SEPARATE_TABLES 128 /* forward: never combine the tables */
 
 /* A (BW, H, N, 32) tensor of 16-bit elements with unit stride along the last axis.
  * Strides are in elements. */
@@ -84,6 +93,9 @@ typedef struct fwa2_fwd_args {
   const void* bias;         /* (H, N, bias_row_stride) or NULL */
   const void* mask;         /* (n_windows, N, mask_row_stride) or NULL */
   int64_t bias_row_stride, mask_row_stride;  /* elements; multiples of 8 */
+  void* workspace;          /* optional scratch of fwa2_fwd_workspace_bytes() bytes, 256-byte aligned;
+                               NULL (or too small) = the kernel reads bias and mask separately */
+  size_t workspace_bytes;
   void* status;             /* optional 16-byte device word block written only on a device-side
                                timeout (must be zero-initialised by the caller); may be NULL */
   int32_t variant;          /* FWA2_FWD_* bits */
@@ -134,6 +146,13 @@ int fwa2_last_cuda_error(void);
 
 /* Forward pass on `stream` (a cudaStream_t). */
 int fwa2_forward(const fwa2_fwd_args* args, void* stream);
+
+/* Bytes of workspace the forward pass would USE for this problem and these variant bits; 0 when it
+ * has no use for one (no bias or no mask, other window sizes, too few images per window type and
+ * FWA2_FWD_COMBINE_TABLES not set).  The forward never requires a workspace: without one it reads
+ * the two tables separately, with the same results up to the rounding of (bias + mask) in fp32. */
+size_t fwa2_fwd_workspace_bytes(int32_t bw, int32_t heads, int32_t n, int32_t n_windows,
+                                int32_t has_bias, int32_t has_mask, int32_t variant);
 
 /* Scratch bytes the backward pass needs for the given problem (0 on invalid sizes). */
 size_t fwa2_bwd_workspace_bytes(int32_t bw, int32_t heads, int32_t n, int32_t n_windows,

@@ -50,6 +50,25 @@ def test_abi_version_and_strerror(lib):
     assert b"head dimension" in lib.fwa2_strerror(-3)
 
 
+def test_forward_workspace_size_needs_no_device(lib):
+    """The forward asks for scratch (one fp32 table bias + mask per window type and head) only for
+    windows of 129 to 256 tokens with both tables, and then only when told to or when every table
+    serves enough images to pay for the pass that builds it."""
+    f = lib.fwa2_fwd_workspace_bytes
+    table = 64 * 3 * 256 * 256 * 4
+    assert f(64 * 64, 3, 256, 64, 1, 1, 0) == table             # 64 images per window type
+    assert f(8 * 64, 3, 256, 64, 1, 1, 0) == 0                  # 8 images: separate tables
+    assert f(8 * 64, 3, 256, 64, 1, 1, _lib.FWA2_FWD_COMBINE_TABLES) == table
+    assert f(64 * 64, 3, 256, 64, 1, 1, _lib.FWA2_FWD_SEPARATE_TABLES) == 0
+    assert f(64 * 64, 3, 256, 64, 1, 1, _lib.FWA2_FWD_GENERAL_KERNEL) == 0
+    assert f(64 * 64, 3, 256, 64, 0, 1, 0) == 0 and f(64 * 64, 3, 256, 64, 1, 0, 0) == 0
+    assert f(64 * 64, 3, 64, 64, 1, 1, 64) == 0 and f(64 * 64, 3, 128, 64, 1, 1, 64) == 0
+    assert f(64 * 64, 3, 257, 64, 1, 1, 64) == 0
+    assert f(40 * 4, 2, 144, 4, 1, 1, 0) == 4 * 2 * 144 * 160 * 4    # rows of 144 padded to 160 floats
+    assert f(4097, 3, 256, 64, 1, 1, 64) == 0                   # BW no multiple of the window types
+    assert f(0, 3, 256, 64, 1, 1, 64) == 0
+
+
 def _fwd_args(**kw):
     a = _lib.FwdArgs()
     a.struct_size = C.sizeof(_lib.FwdArgs)

@@ -319,6 +319,86 @@ def test_token_counts_that_are_no_squares(n, dtype, dev):
     assert np.abs(_f(lse)[..., :n] - ref["lse"]).max() < (4e-2 if dtype == torch.bfloat16 else 5e-3)
 
 
+@pytest.mark.parametrize("window,dtype,batch,nw,heads", [
+    (16, "bf16", 5, 16, 3), (16, "fp16", 3, 4, 6), (12, "bf16", 9, 4, 2), (13, "fp16", 2, 16, 3), (15, "bf16", 40, 1, 1),
+], ids=["n256_bf16", "n256_fp16", "n144", "n169", "n225_one_window_type"])
+def test_forward_with_the_combined_table(window, dtype, batch, nw, heads, dev):
+    """Windows of 129 to 256 tokens with bias AND mask: the forward may add the two tables once per
+    call into one fp32 table per (window type, head) and walk the units table by table (variant bit
+    64 forces it, 128 forbids it; without either the image count decides).  bias + mask is exact in
+    fp32 for a Swin mask (0 / -100 against a bias below 16), so both ways agree bitwise; against
+    the oracle within the usual tolerance."""
+    from flash_window_attention_v2_b200 import kernels as K
+    w = Workload(f"w{window}", batch=batch, nw=nw, heads=heads, window=window, dtype=dtype)
+    got, ref, ins = run_case(w, dev, via="boundary", variant=64)
+    check(w, got, ref, ins)
+    t = make_inputs(w, seed=0, device=dev)
+    res = [K._flash_attn_forward(t["q"], t["k"], t["v"], t["logit_scale"], bias=t["bias"], mask=t["mask"],
+                                 scale_type="tensor", _variant=v) for v in (64, 128)]
+    K.check_device_status(dev)
+    assert torch.equal(res[0][0], res[1][0])
+    assert torch.equal(res[0][1][..., :w.n], res[1][1][..., :w.n])
+
+
+def test_forward_with_the_combined_table_and_an_arbitrary_mask(dev):
+    """A mask of arbitrary real values (not 0 / -100): (bias + mask) rounded once in fp32 and then
+    fused into scale * cos + table differs from adding the two one after the other by an fp32
+    rounding at most, far inside the tolerance; masks of -inf stay -inf."""
+    from flash_window_attention_v2_b200 import kernels as K
+    g = torch.Generator(device="cpu").manual_seed(11)
+    n, bw, h, nw = 208, 12, 3, 4
+    q, k, v = (torch.randn(bw, h, n, 32, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+    bias = (16 * torch.sigmoid(torch.randn(h, n, n, generator=g))).to(torch.bfloat16).to(dev)
+    mask = 3.0 * torch.randn(nw, n, n, generator=g)
+    mask[torch.rand(nw, n, n, generator=g) < 0.1] = float("-inf")
+    mask[:, torch.arange(n), torch.arange(n)] = 0
+    mask = mask.to(torch.bfloat16).to(dev)
+    ls = torch.full((h, 1, 1), math.log(10.0)).to(torch.bfloat16).to(dev)
+    (o1, l1, _), (o0, l0, _) = (K._flash_attn_forward(q, k, v, ls, bias=bias, mask=mask, scale_type="tensor", _variant=x)
+                                for x in (64, 128))
+    K.check_device_status(dev)
+    assert float((l1[..., :n] - l0[..., :n]).abs().max()) < 1e-4
+    assert float((o1.float() - o0.float()).abs().max()) < 2e-2
+    ref = orc.forward_backward(_f(q), _f(k), _f(v), _f(q), _f(ls), _f(bias), _f(mask), dtype=np.float32)
+    assert orc.rel_err(_f(o1), ref["o"]) < TOL["bf16"]["o"]
+    assert np.abs(_f(l1)[..., :n] - ref["lse"]).max() < 4e-2
+
+
+def test_forced_combined_table_without_workspace_is_refused(dev):
+    """Through the C ABI: variant bit 64 with no workspace returns FWA2_ERR_WORKSPACE before
+    anything is launched; without the bit the same call runs on the two separate tables."""
+    import ctypes as C
+    from flash_window_attention_v2_b200 import _lib
+    from flash_window_attention_v2_b200 import kernels as K
+    w = Workload("w16", batch=2, nw=4, heads=2, window=16, dtype="bf16")
+    t = make_inputs(w, seed=0, device=dev)
+    o, lse = torch.empty_like(t["q"]), torch.empty(w.bw, w.heads, 256, device=dev)
+    a = _lib.FwdArgs()
+    a.struct_size, a.abi_version = C.sizeof(_lib.FwdArgs), _lib.FWA2_ABI_VERSION
+    a.dtype, a.bw, a.heads, a.n, a.head_dim, a.n_windows = 1, w.bw, w.heads, w.n, 32, w.nw
+    for dst, x in ((a.q, t["q"]), (a.k, t["k"]), (a.v, t["v"]), (a.o, o)):
+        dst.ptr, dst.stride_bw, dst.stride_h, dst.stride_n = x.data_ptr(), x.stride(0), x.stride(1), x.stride(2)
+    a.lse, a.lse_stride_bw, a.lse_stride_h = lse.data_ptr(), lse.stride(0), lse.stride(1)
+    a.logit_scale, a.scale_is_tensor = t["logit_scale"].data_ptr(), 1
+    a.bias, a.mask, a.bias_row_stride, a.mask_row_stride = t["bias"].data_ptr(), t["mask"].data_ptr(), w.n, w.n
+    L = _lib.lib()
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    assert L.fwa2_fwd_workspace_bytes(w.bw, w.heads, w.n, w.nw, 1, 1, 0) == 0          # two images: not worth it
+    need = L.fwa2_fwd_workspace_bytes(w.bw, w.heads, w.n, w.nw, 1, 1, 64)
+    assert need == w.nw * w.heads * 256 * 256 * 4
+    a.variant = 64
+    assert L.fwa2_forward(C.byref(a), stream) == -7
+    ws = torch.empty(need - 256, dtype=torch.uint8, device=dev)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), need - 256
+    assert L.fwa2_forward(C.byref(a), stream) == -7
+    a.variant, a.workspace, a.workspace_bytes = 0, None, 0
+    assert L.fwa2_forward(C.byref(a), stream) == 0
+    torch.cuda.synchronize(dev)
+    ref = K._flash_attn_forward(t["q"], t["k"], t["v"], t["logit_scale"], bias=t["bias"], mask=t["mask"],
+                                scale_type="tensor", _variant=128)
+    assert torch.equal(o, ref[0])
+
+
 def test_forward_rows_without_any_admissible_key(dev):
     """The reference's own benchmark inputs (masks of 0 / -inf drawn at random, N(0, 1) logit scale):
     both forward kernels agree on which rows have lse = -inf and on everything else."""
